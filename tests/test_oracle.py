@@ -1,0 +1,99 @@
+"""Pins the CPU oracle (Python and C) to the committed outputs of the reference's
+own fp32 recurrence, and pins the chunked WY/UT algebra to the token loop."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+from conftest import GOLDEN_CASES, TOKEN_NAMES, load_golden
+
+from oracle import c_oracle
+from oracle.wkv7_oracle import (chunked_wy_f64, logits_from_retention, max_err_over_rms,
+                                relative_rmse, retention_from_logits, wkv7_oracle, wkv7_oracle_f64)
+
+
+def _run(fn, case, **kw):
+    return fn(*(case[n] for n in TOKEN_NAMES), state_pool=case["state_pool"],
+              cu_seqlens=case["cu_seqlens"], state_indices=case["state_indices"],
+              scale=case["scale"], decay_bias=case["decay_bias"], **kw)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_python_oracle_matches_reference_outputs(name):
+    case = load_golden(name)
+    y, pool = _run(wkv7_oracle, case)
+    # same fp32 arithmetic, possibly a different summation order inside the matmul
+    assert max_err_over_rms(y, case["y"].float()) < (2e-3 if name == "rl_infctx_fp16" else 2e-5)
+    assert max_err_over_rms(pool, case["final_pool"]) < 2e-5
+    touched = set(case["state_indices"].tolist())
+    for slot in range(case["state_pool"].shape[0]):
+        if slot not in touched:
+            assert torch.equal(pool[slot], case["state_pool"][slot])
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_c_oracle_matches_reference_outputs(name):
+    case = load_golden(name)
+    for f64 in (False, True):
+        y, pool = _run(c_oracle.wkv7_oracle_c, case, f64=f64)
+        assert max_err_over_rms(y, case["y"].float()) < (2e-3 if name == "rl_infctx_fp16" else 2e-5)
+        assert max_err_over_rms(pool, case["final_pool"]) < 2e-5
+
+
+def test_rl_infctx_output_rounding():
+    # that reference variant rounds y to the token dtype (rl_infctx/test.py:52-55)
+    case = load_golden("rl_infctx_fp16")
+    y, _ = _run(wkv7_oracle, case)
+    assert relative_rmse(y.half(), case["y"]) < 1e-3
+
+
+def test_retention_mode_equals_logits_mode():
+    torch.manual_seed(3)
+    T, H = 40, 2
+    logits = torch.randn(T, H, 64) * 2
+    toks = [torch.randn(T, H, 64) * 0.3 for _ in range(5)]
+    r, k, v, a, b = toks
+    pool = torch.randn(2, H, 64, 64) * 0.1
+    kw = dict(state_pool=pool, cu_seqlens=[0, 25, 40], state_indices=[1, 0])
+    y0, p0 = wkv7_oracle_f64(r, logits, k, v, a, b, decay_mode="logits", **kw)
+    w = retention_from_logits(logits.double())
+    y1, p1 = wkv7_oracle_f64(r, w, k, v, a, b, decay_mode="retention", **kw)
+    assert max_err_over_rms(y1, y0) < 1e-12 and max_err_over_rms(p1, p0) < 1e-12
+    back = logits_from_retention(w)
+    assert (back - logits.double()).abs().max() < 1e-9
+
+
+def test_c_oracle_threads_and_modes_agree():
+    torch.manual_seed(5)
+    T, H = 70, 3
+    x = torch.rand(T, H, 64) * 4.5 - 5
+    w = torch.exp(-torch.exp(x))
+    r, k, v = (torch.randn(T, H, 64) for _ in range(3))
+    kk = torch.nn.functional.normalize(torch.randn(T, H, 64), dim=-1)
+    a, b = -kk, kk * torch.sigmoid(torch.randn(T, H, 64))
+    pool = torch.randn(3, H, 64, 64) * 0.1
+    kw = dict(state_pool=pool, cu_seqlens=[0, 1, 6, 70], state_indices=[2, 0, 1], decay_mode="retention")
+    y_py, p_py = wkv7_oracle(r, w, k, v, a, b, **kw)
+    y1, p1 = c_oracle.wkv7_oracle_c(r, w, k, v, a, b, n_threads=1, **kw)
+    y4, p4 = c_oracle.wkv7_oracle_c(r, w, k, v, a, b, n_threads=4, **kw)
+    assert torch.equal(y1, y4) and torch.equal(p1, p4)
+    assert max_err_over_rms(y1, y_py) < 2e-5 and max_err_over_rms(p1, p_py) < 2e-5
+
+
+@pytest.mark.parametrize("T", (1, 17, 64, 65, 200))
+def test_chunked_wy_form_equals_token_loop(T):
+    rng = np.random.default_rng(T)
+    w = np.exp(-np.exp(rng.uniform(-5, -0.5, (T, 64))))
+    r, k, v = (rng.standard_normal((T, 64)) for _ in range(3))
+    kk = rng.standard_normal((T, 64))
+    kk /= np.linalg.norm(kk, axis=-1, keepdims=True)
+    a, b = -kk, kk / (1 + np.exp(-rng.standard_normal((T, 64))))
+    S0 = rng.standard_normal((64, 64)) * 0.1
+    y, S = chunked_wy_f64(r, w, k, v, a, b, S0, scale=0.7)
+    tt = lambda x: torch.from_numpy(x).unsqueeze(1)
+    y_ref, p_ref = wkv7_oracle_f64(tt(r), tt(w), tt(k), tt(v), tt(a), tt(b),
+                                   state_pool=torch.from_numpy(S0)[None, None], cu_seqlens=[0, T],
+                                   state_indices=[0], scale=0.7, decay_mode="retention")
+    assert max_err_over_rms(torch.from_numpy(y), y_ref[:, 0]) < 1e-9
+    assert max_err_over_rms(torch.from_numpy(S), p_ref[0, 0]) < 1e-9
