@@ -1,0 +1,96 @@
+// Device-side validation of packed-sequence metadata for the WKV7 state pool.
+//
+// Behaviour follows rwkv-rs/FlashRWKV2 csrc/validation/recurrent_metadata.cu:24-132:
+// the same six error bits, the same status word {error, active tokens, active
+// sequences} with the counts zeroed on error, optional snapshots that are what gets
+// validated, and optional live active counts (the CUDA-graph form).  One CTA of 1024
+// threads; the slot scratch is cleared with 128-bit stores.
+#include "../../common.cuh"
+
+namespace frwkv {
+namespace {
+
+constexpr int kThreads = 1024;
+
+__global__ void __launch_bounds__(kThreads) validate_metadata_kernel(
+    const int* __restrict__ cu, const int* __restrict__ slots, int n_seq_cap, int tok_cap,
+    int pool_size, int max_seqlen, const int* __restrict__ n_active_tok,
+    const int* __restrict__ n_active_seq, int* __restrict__ status, int* __restrict__ seen,
+    int* __restrict__ cu_snap, int* __restrict__ slots_snap) {
+  __shared__ int s_err, s_tok, s_seq;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int tok = n_active_tok ? n_active_tok[0] : tok_cap;
+    int seq = n_active_seq ? n_active_seq[0] : n_seq_cap;
+    int err = 0;
+    if (tok < 0 || tok > tok_cap || seq < 0 || seq > n_seq_cap || ((tok == 0) != (seq == 0))) {
+      err = FRWKV_META_BAD_ACTIVE_COUNT;
+      tok = 0;
+      seq = 0;
+    }
+    s_err = err;
+    s_tok = tok;
+    s_seq = seq;
+  }
+  // clear the duplicate-detection scratch
+  {
+    const int vec = ((reinterpret_cast<uintptr_t>(seen) & 15) == 0) ? pool_size / 4 : 0;
+    int4* seen4 = reinterpret_cast<int4*>(seen);
+    for (int i = tid; i < vec; i += kThreads) seen4[i] = make_int4(-1, -1, -1, -1);
+    for (int i = vec * 4 + tid; i < pool_size; i += kThreads) seen[i] = -1;
+  }
+  if (cu_snap != nullptr) {
+    for (int i = tid; i <= n_seq_cap; i += kThreads) cu_snap[i] = cu[i];
+    for (int i = tid; i < n_seq_cap; i += kThreads) slots_snap[i] = slots[i];
+  }
+  __syncthreads();
+  const int* vcu = cu_snap ? cu_snap : cu;
+  const int* vslots = cu_snap ? slots_snap : slots;
+  const int tok = s_tok, seq = s_seq;
+  if (tid == 0 && s_err == 0 && (vcu[0] != 0 || vcu[seq] != tok)) atomicOr(&s_err, FRWKV_META_BAD_ENDPOINT);
+  int err = 0;
+  for (int i = tid; i < seq; i += kThreads) {
+    const int lo = vcu[i], hi = vcu[i + 1];
+    if (lo < 0 || hi <= lo || hi > tok) {
+      err |= FRWKV_META_BAD_RANGE;
+    } else if (hi - lo > max_seqlen) {
+      err |= FRWKV_META_SEQUENCE_TOO_LONG;
+    }
+    const int slot = vslots[i];
+    if (slot < 0 || slot >= pool_size) {
+      err |= FRWKV_META_BAD_SLOT;
+    } else if (atomicCAS(seen + slot, -1, i) != -1) {
+      err |= FRWKV_META_DUPLICATE_SLOT;
+    }
+  }
+  if (err != 0) atomicOr(&s_err, err);
+  __syncthreads();
+  if (tid == 0) {
+    status[0] = s_err;
+    status[1] = s_err == 0 ? tok : 0;
+    status[2] = s_err == 0 ? seq : 0;
+  }
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_sm100_wkv7_validate_metadata(
+    const int32_t* cu_seqlens, const int32_t* slots, int n_seq_capacity, int token_capacity,
+    int pool_size, int max_seqlen, const int32_t* n_active_tokens,
+    const int32_t* n_active_sequences, int32_t* status, int32_t* seen_slots,
+    int32_t* cu_snapshot, int32_t* slots_snapshot, void* stream) {
+  using namespace frwkv;
+  if (!cu_seqlens || !slots || !status || !seen_slots)
+    return fail(FRWKV_ERR_ARGUMENT, "validate_metadata: cu_seqlens, slots, status and seen_slots must be non-null");
+  if ((cu_snapshot == nullptr) != (slots_snapshot == nullptr))
+    return fail(FRWKV_ERR_ARGUMENT, "validate_metadata: pass both snapshots or neither");
+  if (n_seq_capacity <= 0 || n_seq_capacity > 65535)
+    return fail(FRWKV_ERR_ARGUMENT, "validate_metadata: sequence count must be in 1..65535, got %d", n_seq_capacity);
+  if (token_capacity <= 0 || pool_size <= 0 || max_seqlen <= 0)
+    return fail(FRWKV_ERR_ARGUMENT, "validate_metadata: token_capacity, pool_size and max_seqlen must be positive");
+  validate_metadata_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      cu_seqlens, slots, n_seq_capacity, token_capacity, pool_size, max_seqlen, n_active_tokens,
+      n_active_sequences, status, seen_slots, cu_snapshot, slots_snapshot);
+  return check_launch("validate_metadata");
+}

@@ -1,0 +1,116 @@
+/* C ABI of the sm_100a (B200) WKV7 backend: libfrwkv_sm100.so.
+ *
+ * Every entry takes raw device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream and returns an int: 0 = launched, nonzero = the
+ * arguments were rejected and nothing was launched (frwkv_sm100_last_error()
+ * gives the reason).  Unless an entry's comment says otherwise the library
+ * owns nothing, allocates nothing and never synchronises; no entry throws.
+ *
+ * Each entry cites the interface of rwkv-rs/FlashRWKV2 it stands in for
+ * (paths inside that project).
+ *
+ * Layouts (identical to the reference):
+ *   token tensors r, w, k, v, a, b, y : [total_tokens, H, 64], contiguous,
+ *       bf16 / fp16 (the reference's contract) or fp32 (verification mode);
+ *   state pool                       : [slots, H, 64(key), 64(value)] fp32,
+ *       element (k, v) at k*64+v, updated in place at `slots[seq]` only;
+ *   cu_seqlens [n_seq+1], slots [n_seq], status [3] : int32.
+ *   status = {error bitmask, active tokens, active sequences}.
+ */
+#ifndef FRWKV_SM100_H_
+#define FRWKV_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FRWKV_SM100_ABI_VERSION 1
+
+/* token dtype of r,w,k,v,a,b,y */
+enum { FRWKV_IO_BF16 = 0, FRWKV_IO_FP16 = 1, FRWKV_IO_FP32 = 2 };
+/* meaning of w: raw decay logits (the reference's contract:
+ * rho = exp(-exp(-1/2) * sigmoid(w + bias)), csrc/sm120/tmix/wkv7/recurrent_decay.cuh:18-23)
+ * or the retention rho itself (how the benchmark workloads are specified). */
+enum { FRWKV_DECAY_LOGITS = 0, FRWKV_DECAY_RETENTION = 1 };
+/* metadata error bits written to status[0]; same values as
+ * csrc/validation/recurrent_metadata.cu:15-22 */
+enum {
+  FRWKV_META_BAD_ENDPOINT = 1 << 0,
+  FRWKV_META_BAD_RANGE = 1 << 1,
+  FRWKV_META_BAD_SLOT = 1 << 2,
+  FRWKV_META_DUPLICATE_SLOT = 1 << 3,
+  FRWKV_META_BAD_ACTIVE_COUNT = 1 << 4,
+  FRWKV_META_SEQUENCE_TOO_LONG = 1 << 5,
+};
+/* prefill strategy */
+enum { FRWKV_PREFILL_AUTO = 0, FRWKV_PREFILL_RECURRENT = 1, FRWKV_PREFILL_CHUNK_TC = 2 };
+/* return codes */
+enum {
+  FRWKV_OK = 0,
+  FRWKV_ERR_ARGUMENT = 1,
+  FRWKV_ERR_UNSUPPORTED = 2,
+  FRWKV_ERR_WORKSPACE = 3,
+  FRWKV_ERR_CUDA = 4,
+};
+
+int frwkv_sm100_abi_version(void);
+/* Message for the last nonzero return on the calling thread ("" if none). */
+const char* frwkv_sm100_last_error(void);
+
+/* Device-side metadata validation; stands in for validate_recurrent_metadata_kernel
+ * and its launchers (csrc/validation/recurrent_metadata.cu:24-132,196-225).
+ * One launch.  Checks the end points, strictly increasing non-empty ranges,
+ * slot bounds, duplicate slots and the active counts; writes status[3].
+ *   n_active_tokens / n_active_sequences : device scalars or NULL (= capacities);
+ *   seen_slots   : scratch of pool_size int32;
+ *   cu_snapshot / slots_snapshot : both NULL, or buffers of n_seq_capacity+1 /
+ *       n_seq_capacity int32 that receive a copy which is then what is validated. */
+int frwkv_sm100_wkv7_validate_metadata(
+    const int32_t* cu_seqlens, const int32_t* slots, int n_seq_capacity, int token_capacity,
+    int pool_size, int max_seqlen, const int32_t* n_active_tokens,
+    const int32_t* n_active_sequences, int32_t* status, int32_t* seen_slots,
+    int32_t* cu_snapshot, int32_t* slots_snapshot, void* stream);
+
+/* Register-streaming recurrence (decode and short rows); stands in for
+ * tmix_wkv7_recurrent_fp32_from_decay_logits_cuda and the kernels it selects
+ * (csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.cu:90-281,457-517).
+ * Fail-closed like the reference (:116-123): status[0] != 0 fills y with NaN and
+ * leaves the pool untouched; sequences at or beyond status[2] are skipped.
+ *   status     : device int32[3], or NULL to trust the metadata (all n_seq active);
+ *   decay_bias : [H*64] in the token dtype or NULL (logits mode only);
+ *   y_f32      : optional fp32 copy of y before rounding (verification), or NULL;
+ *   max_seqlen : largest sequence length (a launch-shape hint; <= 0 if unknown). */
+int frwkv_sm100_wkv7_recurrent(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* decay_bias, void* y, float* y_f32, int n_seq, int total_tokens, int heads,
+    int io_dtype, int decay_mode, float scale, int max_seqlen, void* stream);
+
+/* Chunked prefill (chunk 64, WY/UT transform on tcgen05 tensor cores, fp32 state
+ * carry), in place on the pool; stands in for the kernels behind
+ * rl_infctx_tmix_wkv7_chunk_fp32io16_forward
+ * (csrc/sm120/tmix/wkv7/rl_infctx_chunk_fp32io16_forward.cu:41-135,318-539 and
+ * rl_infctx_chunk_fp32io16_backward.cu:47-128), taking cu_seqlens directly
+ * instead of host-built per-chunk metadata.  Same fail-closed rules as above.
+ *   strategy   : FRWKV_PREFILL_AUTO picks the tensor-core kernel for 16-bit
+ *                tokens and long rows, else the register-streaming recurrence;
+ *   workspace  : device scratch of at least
+ *                frwkv_sm100_wkv7_prefill_workspace_bytes() bytes (may be NULL if 0);
+ *   error_flag : optional device int32 that the tensor-core kernel sets nonzero if
+ *                one of its bounded waits gave up (the output is then invalid). */
+int frwkv_sm100_wkv7_prefill(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* decay_bias, void* y, float* y_f32, int n_seq, int total_tokens, int heads,
+    int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy, void* workspace,
+    size_t workspace_bytes, int32_t* error_flag, void* stream);
+
+size_t frwkv_sm100_wkv7_prefill_workspace_bytes(int n_seq, int total_tokens, int heads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRWKV_SM100_H_ */

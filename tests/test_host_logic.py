@@ -1,0 +1,184 @@
+"""CPU-only checks: backend selection, the C-ABI library's exports, wrapper argument
+rejection (before any launch), workload generation and sequence sharding."""
+
+from __future__ import annotations
+
+import ctypes
+import inspect
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_backend_selection_by_capability():
+    import flashrwkv2_b200 as pkg
+
+    assert pkg._backend_module_name((10, 0)) == "_C_sm100"
+    assert pkg._backend_module_name((10, 3)) == "_C_sm100"
+    for capability in ((9, 0), (12, 0), (8, 0)):
+        with pytest.raises(RuntimeError, match="no binary-compatible native backend"):
+            pkg._backend_module_name(capability)
+
+
+def test_backend_not_loaded_without_cuda(monkeypatch):
+    import flashrwkv2_b200 as pkg
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    assert pkg._load_native_backend() is None
+
+
+def test_backend_loader_reports_missing_extension(monkeypatch):
+    import flashrwkv2_b200 as pkg
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "get_device_capability", lambda *a: (10, 0))
+    monkeypatch.setattr(pkg, "_NATIVE_BACKENDS", (((10, 0), "_C_missing"),))
+    with pytest.raises(RuntimeError, match="not built or cannot be loaded"):
+        pkg._load_native_backend()
+
+
+def test_operators_fail_loudly_without_backend(monkeypatch):
+    """No CPU fallback: with no backend loaded the operator raises instead of computing."""
+    import flashrwkv2_b200 as pkg
+    from flashrwkv2_b200.tmix import wkv7
+
+    monkeypatch.setattr(pkg, "_C", None)
+    t = torch.zeros(2, 1, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        wkv7.infer_tmix_wkv7_recurrent_fp32io16_forward_varlen(
+            t, t, t, t, t, t, state_pool=torch.zeros(1, 1, 64, 64), cu_seqlens=torch.tensor([0, 2], dtype=torch.int32),
+            state_indices=torch.tensor([0], dtype=torch.int32))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    from flashrwkv2_b200 import _lib
+    from flashrwkv2_b200.build import build
+
+    build()
+    header = (ROOT / "include" / "frwkv_sm100.h").read_text()
+    declared = set(re.findall(r"\b(frwkv_sm100_\w+)\s*\(", header))
+    assert declared == set(_lib.SYMBOLS)
+    lib = _lib.load()
+    assert isinstance(lib, ctypes.CDLL)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.frwkv_sm100_abi_version() == _lib.ABI_VERSION
+    # argument rejection needs no GPU: null pointers are refused before any launch
+    rc = lib.frwkv_sm100_wkv7_recurrent(*([0] * 13), 1, 1, 1, 0, 0, 1.0, 1, 0)
+    assert rc != 0 and "non-null" in _lib.last_error()
+    rc = lib.frwkv_sm100_wkv7_prefill(*([0] * 13), 1, 1, 1, 0, 0, 1.0, 1, 0, 0, 0, 0, 0)
+    assert rc != 0
+    assert lib.frwkv_sm100_wkv7_prefill_workspace_bytes(1, 64, 1) >= 0
+
+
+def test_native_module_exports_reference_symbols():
+    from flashrwkv2_b200 import _C_sm100 as ext
+
+    for name in ("prepare_tmix_wkv7_recurrent_metadata", "prepare_tmix_wkv7_recurrent_graph_metadata",
+                 "tmix_wkv7_recurrent_fp32_from_decay_logits", "rl_infctx_tmix_wkv7_chunk_fp32io16_forward",
+                 "_RecurrentMetadataTicket", "tmix_wkv7_prefill_fp32"):
+        assert hasattr(ext, name), name
+    sig = inspect.signature(ext.tmix_wkv7_recurrent_fp32_from_decay_logits)
+    assert list(sig.parameters)[:14] == ["query_start_loc", "state_indices", "state", "r", "decay_logits", "k", "v",
+                                         "a", "b", "output", "scale", "decay_bias", "validated_metadata",
+                                         "max_seqlen"]
+    sig = inspect.signature(ext.rl_infctx_tmix_wkv7_chunk_fp32io16_forward)
+    assert list(sig.parameters)[:13] == ["sequence_chunk_offsets", "chunk_token_starts", "chunk_token_ends", "state",
+                                         "r", "decay_logits", "k", "v", "a", "b", "strategy", "scale", "decay_bias"]
+    for method in ("_check_compatible", "_query_start_loc_snapshot", "_state_indices_snapshot", "_status",
+                   "_max_seqlen", "_is_graph", "_num_active_tokens", "_num_active_sequences"):
+        assert hasattr(ext._RecurrentMetadataTicket, method)
+
+
+def test_public_signature_matches_reference_contract():
+    from flashrwkv2_b200.tmix.wkv7 import infer_tmix_wkv7_recurrent_fp32io16_forward_varlen as op
+
+    params = inspect.signature(op).parameters
+    for name in ("r", "decay_logits", "k", "v", "a", "b", "state_pool", "cu_seqlens", "state_indices", "scale",
+                 "decay_bias", "max_seqlen", "validated_metadata"):
+        assert name in params
+    with pytest.raises(TypeError, match="log_decay"):
+        op(None, None, None, None, None, None, state_pool=None, cu_seqlens=None, log_decay=None)
+
+
+def test_wrapper_rejections_happen_before_any_launch():
+    from flashrwkv2_b200.tmix import wkv7
+    from flashrwkv2_b200.tmix.wkv7.rl_infctx import rl_infctx_tmix_wkv7_chunk_fp32io16 as chunk
+
+    t = torch.zeros(4, 2, 64, dtype=torch.bfloat16)
+    pool = torch.zeros(2, 2, 64, 64)
+    cu = torch.tensor([0, 4], dtype=torch.int32)
+    slots = torch.tensor([0], dtype=torch.int32)
+    op = wkv7.infer_tmix_wkv7_recurrent_fp32io16_forward_varlen
+    with pytest.raises(TypeError, match="r must be a torch.Tensor"):
+        op(None, t, t, t, t, t, state_pool=pool, cu_seqlens=cu, state_indices=slots)
+    with pytest.raises(ValueError, match="packed shape"):
+        op(t[0], t, t, t, t, t, state_pool=pool, cu_seqlens=cu, state_indices=slots)
+    with pytest.raises(ValueError, match="contiguous"):
+        op(t.transpose(0, 1), t, t, t, t, t, state_pool=pool, cu_seqlens=cu, state_indices=slots)
+    with pytest.raises(TypeError, match="float32"):
+        op(t, t, t, t, t, t, state_pool=pool.half(), cu_seqlens=cu, state_indices=slots)
+    with pytest.raises(ValueError, match="one-dimensional"):
+        op(t, t, t, t, t, t, state_pool=pool, cu_seqlens=cu.reshape(1, -1), state_indices=slots)
+    with pytest.raises(ValueError, match="total_tokens is required"):
+        wkv7.prepare_tmix_wkv7_recurrent_metadata(cu, slots, state_pool_size=2)
+    with pytest.raises(ValueError, match="capacity arguments"):
+        wkv7.prepare_tmix_wkv7_recurrent_metadata(cu, slots, state_pool_size=2, total_tokens=4, token_capacity=4)
+    with pytest.raises(ValueError, match="all graph metadata"):
+        wkv7.prepare_tmix_wkv7_recurrent_metadata(cu, slots, state_pool_size=2, token_capacity=4)
+    with pytest.raises(ValueError, match="chunk_size"):
+        chunk(t, t, t, t, t, t, cu_seqlens=cu, chunk_size=48)
+    with pytest.raises(ValueError, match="strategy"):
+        chunk(t, t, t, t, t, t, cu_seqlens=cu, strategy="fast")
+    with pytest.raises(ValueError, match="finite"):
+        chunk(t, t, t, t, t, t, cu_seqlens=cu, scale=float("nan"))
+    with pytest.raises(ValueError, match="contiguous CUDA"):
+        chunk(t, t, t, t, t, t, cu_seqlens=cu)
+
+
+def test_workloads_are_seeded_and_shaped():
+    from flashrwkv2_b200.workloads import describe, make_workload
+
+    c0 = make_workload("c0")
+    assert c0.tensors["r"].shape == (64, 32, 64) and c0.tensors["r"].dtype == torch.float32
+    assert float(c0.tensors["state_pool"].abs().max()) == 0.0
+    again = make_workload("c0")
+    assert all(torch.equal(c0.tensors[n], again.tensors[n]) for n in "rwkvab")
+    w = c0.tensors["w"]
+    assert float(w.min()) > 0.54 and float(w.max()) < 0.9934
+    kk = -c0.tensors["a"]
+    assert torch.allclose(kk.norm(dim=-1), torch.ones(64, 32), atol=1e-5)
+    c1 = make_workload("c1", n_seq=8, heads=2)
+    assert c1.tensors["r"].dtype == torch.bfloat16 and c1.tensors["cu_seqlens"].tolist() == list(range(9))
+    c3 = make_workload("c3", with_tensors=False)
+    assert c3.n_seq == 64 and all(1 <= x <= 8192 for x in c3.lengths)
+    assert make_workload("c3", with_tensors=False).lengths == c3.lengths
+    assert "N=2048" in describe("c4_decode")
+
+
+def test_lpt_sharding_properties():
+    from flashrwkv2_b200.sharding import shard_packed, shard_sequences
+    from flashrwkv2_b200.workloads import make_workload
+
+    lengths = make_workload("c3", with_tensors=False).lengths
+    for world in (1, 2, 4, 8):
+        bins = shard_sequences(lengths, world)
+        assert sorted(i for b in bins for i in b) == list(range(len(lengths)))
+        loads = [sum(lengths[i] for i in b) for b in bins]
+        assert max(loads) - min(loads) <= max(lengths)  # LPT bound
+    assert [len(b) for b in shard_sequences([1] * 2048, 8)] == [256] * 8
+    assert [len(b) for b in shard_sequences([8192] * 64, 8)] == [8] * 8
+    # packed slicing: rows, re-based cu_seqlens, slots
+    cu = torch.tensor([0, 3, 4, 9, 11], dtype=torch.int32)
+    slots = torch.tensor([7, 5, 3, 1], dtype=torch.int32)
+    toks = {"r": torch.arange(11).float().reshape(11, 1, 1).expand(11, 1, 64).contiguous()}
+    parts = [shard_packed(toks, cu, slots, 2, rank) for rank in range(2)]
+    assert sorted(torch.cat([p["rows"] for p in parts]).tolist()) == list(range(11))
+    for p in parts:
+        assert p["cu_seqlens"][0] == 0 and p["cu_seqlens"][-1] == p["r"].shape[0]
+        assert p["state_indices"].tolist() == [slots[i].item() for i in p["sequences"]]
+        assert torch.equal(p["r"][:, 0, 0], p["rows"].float())
