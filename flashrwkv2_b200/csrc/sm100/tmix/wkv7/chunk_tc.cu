@@ -1,10 +1,691 @@
-// placeholder until the tensor-core kernel lands
+// WKV7 chunked prefill on tcgen05 tensor cores (sm_100a): 64-row chunks, WY/UT transform,
+// fp32 state carried in TMEM.
+//
+// One CTA (256 threads) walks one (sequence, head) chunk by chunk.  Per chunk of L <= 64 rows,
+// with g_t = prod_{s<=t} rho_s (per key channel; g_{t-1} is the exclusive product):
+//     At = a * g_{t-1}   Bt = b / g_t   Kt = k / g_t   Rt = r * g_t                    [L, K]
+//     P  = [At; Rt] [Bt; Kt]^T  -> A_ab, A_ak (strictly lower), A_rb, A_rk (lower)      [2L, 2L]
+//     Q  = [At; Rt] S0 + [A_ak; A_rk] V     (rows 0..63 = W, rows 64..127 = part of Y)
+//     U  = (I - A_ab)^-1 W                  (U[t] = a_t^T S_{t-1})
+//     Y  = scale * (Q[64..] + A_rb U)
+//     S  = diag(g_L) (S0 + Bt^T U + Kt^T V)
+// which is the token recurrence of rwkv-rs/FlashRWKV2 tests/tmix/wkv7/test.py:66-83 regrouped;
+// the reference computes the same quantities on CUDA cores in
+// csrc/sm120/tmix/wkv7/rl_infctx_chunk_fp32io16_forward.cu:318-539.
+//
+// Precision: every dense contraction is a tcgen05.mma kind::f16 on bf16 operands with fp32
+// accumulation in TMEM.  A single bf16 rounding of the decay-scaled operands is not accurate
+// enough, so each fp32 operand x is split into hi = bf16(x), lo = bf16(x - hi) and a product
+// is issued as hi*hi + hi*lo + lo*hi (about 16 significant bits); V is exact in bf16 and
+// needs no lo part.  The triangular inverse is computed in fp32 on CUDA cores (16x16
+// diagonal blocks by substitution, then block substitution).
+//
+// Data movement: the six token tiles of a chunk arrive by TMA (cp.async.bulk.tensor.3d over
+// the [64, H, T] view of each tensor) into one staging area; operands are written into
+// un-swizzled core-matrix tiles (see tcgen05.cuh) so that the same tile can be read K-major
+// or MN-major; accumulators P (128 columns), Q, U and the state S (64 columns each) live in
+// TMEM.  Rows past the end of a sequence are masked to rho = 1, r = k = a = b = 0.
+// Every wait on an mbarrier is bounded; on a timeout the CTA raises *error_flag, waits
+// (bounded) for its TMA load, frees its TMEM and returns.
 #include "../../common.cuh"
+#include "../../tcgen05.cuh"
+
+#include <cstdlib>
+#include <type_traits>
+
 namespace frwkv {
-size_t chunk_tc_workspace_bytes(int, int, int) { return 0; }
-int launch_chunk_tc(const int32_t*, const int32_t*, const int32_t*, float*, const void*, const void*, const void*,
-                    const void*, const void*, const void*, const void*, void*, float*, int, int, int, int, int, float,
-                    int, void*, size_t, int32_t*, cudaStream_t) {
-  return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_prefill: tensor-core chunk kernel not built");
+namespace {
+
+using namespace tc;
+
+constexpr int kThreads = 256;
+constexpr int kChunk = 64;
+
+// ---- shared-memory map (bytes) -------------------------------------------------------------
+// K-major 128-row tiles (also read MN-major with the strides swapped)
+constexpr uint32_t kRowGroup = 128;              // 8 rows x 16 B
+constexpr uint32_t kChunkStride128 = 16 * 128 + 16;  // stride between 16-byte k-chunks, 128-row tile (padded)
+constexpr uint32_t kTile128 = 8 * kChunkStride128;   // 16512: one bf16 part (hi or lo)
+// MN-major 64-row operand tiles (rows = contraction index, 64 contiguous columns)
+constexpr uint32_t kChunkStride64 = 8 * 128 + 16;    // stride between 16-byte column chunks
+constexpr uint32_t kTile64 = 8 * kChunkStride64;     // 8320
+
+constexpr uint32_t kRawTile = 64 * 128;              // one [64][64] 16-bit tile as TMA writes it
+constexpr uint32_t kOffRaw = 0;                      // r, w, k, v, a, b
+constexpr uint32_t kOffX1 = kOffRaw + 6 * kRawTile;  // [At; Rt] hi, lo  -> later [T; A_rb]
+constexpr uint32_t kOffX2 = kOffX1 + 2 * kTile128;   // [Bt; Kt] hi, lo
+constexpr uint32_t kOffX3 = kOffX2 + 2 * kTile128;   // [A_ak; A_rk] hi, lo
+constexpr uint32_t kOffOp = kOffX3 + 2 * kTile128;   // S0 / W / U operand hi, lo
+constexpr uint32_t kOffV = kOffOp + 2 * kTile64;     // V operand hi, lo
+constexpr uint32_t kOffMisc = kOffV + 2 * kTile64;   // gamma_L[64], partial sums[8][64], barriers
+constexpr uint32_t kMiscBytes = 64 * 4 + 8 * 64 * 4 + 64;
+constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 128;  // + alignment slack
+// fp32 scratch of the triangular inverse, aliased onto the TMA staging area (free after stage A)
+constexpr int kInvLd = 68;                                      // padded row length (floats)
+constexpr uint32_t kOffAb = kOffRaw;                            // A_ab   [64][68]
+constexpr uint32_t kOffTi = kOffAb + 64 * kInvLd * 4;           // T      [64][68]
+constexpr uint32_t kOffMb = kOffTi + 64 * kInvLd * 4;           // block products [3][16][17]
+static_assert(kOffMb + 3 * 16 * 17 * 4 <= kOffX1, "inverse scratch must fit in the staging area");
+
+// ---- TMEM map (columns) --------------------------------------------------------------------
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColP = 0, kColQ = 128, kColU = 192, kColS = 256;
+
+struct ChunkParams {
+  const int* cu;
+  const int* slots;
+  const int* status;
+  float* pool;
+  const void* bias;
+  void* y;
+  float* y_f32;
+  int* error_flag;
+  int n_seq, total_tokens, heads;
+  float scale;
+};
+
+struct Maps {
+  CUtensorMap r, w, k, v, a, b;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo_elem, float hi_elem) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo_elem, hi_elem);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
+__device__ __forceinline__ float bf16_lo_as_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi_as_f32(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+// hi/lo split of 8 consecutive fp32 values into two 16-byte vectors of bf16
+__device__ __forceinline__ void split8(const float* x, uint4& hi, uint4& lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    h[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
+    l[i] = pack_bf16x2(x[2 * i] - bf16_lo_as_f32(h[i]), x[2 * i + 1] - bf16_hi_as_f32(h[i]));
+  }
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+template <typename io_t> __device__ __forceinline__ float2 unpack2(uint32_t packed);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t packed) {
+  return make_float2(bf16_lo_as_f32(packed), bf16_hi_as_f32(packed));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t packed) {
+  return __half22float2(*reinterpret_cast<__half2*>(&packed));
+}
+
+// One dense contraction D (+)= A * B over `ksteps` steps of 16, as hi*hi (+ hi*lo) (+ lo*hi).
+// a_lo_off / b_lo_off: byte distance from the hi part to the lo part (0 = operand has no lo part).
+__device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_addr, uint32_t a_lo_off, uint32_t a_kstep,
+                                           uint32_t a_lbo, uint32_t a_sbo, uint32_t b_addr, uint32_t b_lo_off,
+                                           uint32_t b_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t idesc,
+                                           int ksteps, bool accumulate) {
+  bool acc = accumulate;
+  for (int ks = 0; ks < ksteps; ++ks) {
+    const uint64_t a_hi = smem_desc(a_addr + ks * a_kstep, a_lbo, a_sbo);
+    const uint64_t b_hi = smem_desc(b_addr + ks * b_kstep, b_lbo, b_sbo);
+    mma_f16_ss(tmem_d, a_hi, b_hi, idesc, acc);
+    acc = true;
+    if (b_lo_off != 0) mma_f16_ss(tmem_d, a_hi, smem_desc(b_addr + b_lo_off + ks * b_kstep, b_lbo, b_sbo), idesc, true);
+    if (a_lo_off != 0) mma_f16_ss(tmem_d, smem_desc(a_addr + a_lo_off + ks * a_kstep, a_lbo, a_sbo), b_hi, idesc, true);
+  }
+}
+
+template <typename io_t, bool LOGITS>
+__global__ void __launch_bounds__(kThreads, 1)
+wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte aligned base (TMA destination and descriptor addresses)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3;   // TMEM lane quadrant this warp may access
+  const int half = warp >> 2;  // which half of the columns this warp handles
+
+  if (p.status != nullptr && p.status[0] != 0) {
+    if constexpr (std::is_same<io_t, __nv_bfloat16>::value || std::is_same<io_t, __half>::value) {
+      fill_output_nan(static_cast<io_t*>(p.y), p.y_f32, static_cast<long long>(p.total_tokens) * p.heads * kHeadDim,
+                      static_cast<long long>(blockIdx.x) * kThreads + tid, static_cast<long long>(gridDim.x) * kThreads);
+    }
+    return;
+  }
+  const int active = p.status != nullptr ? p.status[2] : p.n_seq;
+  const int seq = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
+  if (seq >= active || seq >= p.n_seq) return;
+  const int t_begin = p.cu[seq], len = p.cu[seq + 1] - t_begin;
+  if (len <= 0) return;
+  const int n_chunks = (len + kChunk - 1) / kChunk;
+  const int slot = p.slots[seq];
+
+  float* gamma_l = reinterpret_cast<float*>(smem + kOffMisc);
+  float* part = gamma_l + 64;                       // [8][64] log2-decay sums of each 8-row group
+  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(part + 8 * 64);
+  uint64_t* bar_mma = bar_tma + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
+  const uint32_t sbase = smem_u32(smem);
+
+  if (tid == 0) {
+    mbar_init(bar_tma, 1);
+    mbar_init(bar_mma, 1);
+    mbar_fence_init();
+    tma_prefetch_descriptor(&maps.r);
+    tma_prefetch_descriptor(&maps.w);
+    tma_prefetch_descriptor(&maps.k);
+    tma_prefetch_descriptor(&maps.v);
+    tma_prefetch_descriptor(&maps.a);
+    tma_prefetch_descriptor(&maps.b);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+
+  auto issue_tma = [&](int chunk) {  // thread 0 only
+    const int row = t_begin + chunk * kChunk;
+    mbar_expect_tx(bar_tma, 6 * kRawTile);
+    tma_load_3d(smem + kOffRaw + 0 * kRawTile, &maps.r, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 1 * kRawTile, &maps.w, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 2 * kRawTile, &maps.k, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 3 * kRawTile, &maps.v, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 4 * kRawTile, &maps.a, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 5 * kRawTile, &maps.b, bar_tma, 0, head, row);
+  };
+  if (tid == 0) issue_tma(0);
+  bool tma_in_flight = true;
+  uint32_t tma_parity = 0;  // parity of the load in flight
+
+  // ---- initial state: global -> TMEM (fp32) and -> S0 operand tile (hi/lo, MN-major) ----------
+  float* state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
+  if (quad < 2) {
+    const int krow = quad * 32 + lane;
+    uint32_t regs[32];
+    const float4* src = reinterpret_cast<const float4*>(state_g + krow * kHeadDim + half * 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 f = __ldcs(src + i);
+      regs[4 * i] = __float_as_uint(f.x);
+      regs[4 * i + 1] = __float_as_uint(f.y);
+      regs[4 * i + 2] = __float_as_uint(f.z);
+      regs[4 * i + 3] = __float_as_uint(f.w);
+    }
+    tmem_st32(tmem_lane + kColS + half * 32, regs);
+    uint8_t* op = smem + kOffOp + (krow & 7) * 16 + (krow >> 3) * kRowGroup;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 hi, lo;
+      split8(reinterpret_cast<const float*>(regs) + 8 * j, hi, lo);
+      *reinterpret_cast<uint4*>(op + (half * 4 + j) * kChunkStride64) = hi;
+      *reinterpret_cast<uint4*>(op + kTile64 + (half * 4 + j) * kChunkStride64) = lo;
+    }
+    tmem_st_wait();
+  }
+
+  constexpr uint32_t idesc_kk128 = instr_desc_f16(128, 128, kMajorK, kMajorK);
+  constexpr uint32_t idesc_kmn64 = instr_desc_f16(128, 64, kMajorK, kMajorMN);
+  constexpr uint32_t idesc_mnmn64 = instr_desc_f16(128, 64, kMajorMN, kMajorMN);
+  constexpr bool kVExact = std::is_same<io_t, __nv_bfloat16>::value;
+  constexpr uint32_t v_lo_off = kVExact ? 0u : kTile64;
+
+  uint32_t mma_uses = 0;
+  bool failed = false;
+  const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
+
+  for (int c = 0; c < n_chunks; ++c) {
+    const int rows = min(kChunk, len - c * kChunk);
+    const int row0 = t_begin + c * kChunk;
+
+    // ================= stage A: decay products and scaled operands =================
+    {
+      const bool ok = mbar_wait(bar_tma, tma_parity);
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tma_in_flight = false;
+      tma_parity ^= 1u;
+    }
+    {
+      const int kp = lane;       // key channels 2*kp, 2*kp+1
+      const int tg = warp;       // rows 8*tg .. 8*tg+7
+      const uint32_t* raw_r = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 0 * kRawTile);
+      const uint32_t* raw_w = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 1 * kRawTile);
+      const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
+      const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
+      const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
+      float2 bias2 = make_float2(0.f, 0.f);
+      if (bias_g != nullptr) bias2 = make_float2(to_f32(bias_g[2 * kp]), to_f32(bias_g[2 * kp + 1]));
+      float2 lw[8];   // log2(rho) per row
+      float2 run = make_float2(0.f, 0.f);
+      float2 cum[8];  // inclusive sums within this 8-row group
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = tg * 8 + i;
+        const float2 w2 = unpack2<io_t>(raw_w[t * 32 + kp]);
+        float2 l;
+        if constexpr (LOGITS) {
+          l.x = -kRateLog2e / (1.0f + exp2f(-kLog2e * (w2.x + bias2.x)));
+          l.y = -kRateLog2e / (1.0f + exp2f(-kLog2e * (w2.y + bias2.y)));
+        } else {
+          l.x = log2f(w2.x);
+          l.y = log2f(w2.y);
+        }
+        if (t >= rows) l = make_float2(0.f, 0.f);
+        lw[i] = l;
+        run.x += l.x;
+        run.y += l.y;
+        cum[i] = run;
+      }
+      reinterpret_cast<float2*>(part + tg * 64)[kp] = run;
+      __syncthreads();
+      float2 off = make_float2(0.f, 0.f);
+      for (int g = 0; g < tg; ++g) {
+        const float2 s = reinterpret_cast<const float2*>(part + g * 64)[kp];
+        off.x += s.x;
+        off.y += s.y;
+      }
+      uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kChunkStride128 + (kp & 3) * 4;
+      uint8_t* x2 = smem + kOffX2 + (kp >> 2) * kChunkStride128 + (kp & 3) * 4;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = tg * 8 + i;
+        const bool live = t < rows;
+        const float2 lg = make_float2(off.x + cum[i].x, off.y + cum[i].y);
+        const float2 g = make_float2(exp2f(lg.x), exp2f(lg.y));
+        const float2 gi = make_float2(exp2f(-lg.x), exp2f(-lg.y));
+        const float2 gx = make_float2(exp2f(lg.x - lw[i].x), exp2f(lg.y - lw[i].y));
+        float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
+        float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
+        float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
+        float2 b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
+        if (!live) {
+          r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
+        }
+        const float at[2] = {a2.x * gx.x, a2.y * gx.y};
+        const float rt[2] = {r2.x * g.x, r2.y * g.y};
+        const float bt[2] = {b2.x * gi.x, b2.y * gi.y};
+        const float kt[2] = {k2.x * gi.x, k2.y * gi.y};
+        const uint32_t row_off = (t >> 3) * kRowGroup + (t & 7) * 16;          // rows 0..63
+        const uint32_t row_off_hi = ((t + 64) >> 3) * kRowGroup + (t & 7) * 16;  // rows 64..127
+        uint32_t h;
+        h = pack_bf16x2(at[0], at[1]);
+        *reinterpret_cast<uint32_t*>(x1 + row_off) = h;
+        *reinterpret_cast<uint32_t*>(x1 + kTile128 + row_off) = pack_bf16x2(at[0] - bf16_lo_as_f32(h), at[1] - bf16_hi_as_f32(h));
+        h = pack_bf16x2(rt[0], rt[1]);
+        *reinterpret_cast<uint32_t*>(x1 + row_off_hi) = h;
+        *reinterpret_cast<uint32_t*>(x1 + kTile128 + row_off_hi) = pack_bf16x2(rt[0] - bf16_lo_as_f32(h), rt[1] - bf16_hi_as_f32(h));
+        h = pack_bf16x2(bt[0], bt[1]);
+        *reinterpret_cast<uint32_t*>(x2 + row_off) = h;
+        *reinterpret_cast<uint32_t*>(x2 + kTile128 + row_off) = pack_bf16x2(bt[0] - bf16_lo_as_f32(h), bt[1] - bf16_hi_as_f32(h));
+        h = pack_bf16x2(kt[0], kt[1]);
+        *reinterpret_cast<uint32_t*>(x2 + row_off_hi) = h;
+        *reinterpret_cast<uint32_t*>(x2 + kTile128 + row_off_hi) = pack_bf16x2(kt[0] - bf16_lo_as_f32(h), kt[1] - bf16_hi_as_f32(h));
+        if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_l)[kp] = g;
+      }
+      // V operand: rows = token, 64 contiguous value columns (MN-major); bf16 is copied, fp16 is split
+      const uint8_t* raw_v = smem + kOffRaw + 3 * kRawTile;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int id = tid + j * kThreads;  // 512 chunks of 8 values
+        const int s = id >> 3, vc = id & 7;
+        uint4 q = *reinterpret_cast<const uint4*>(raw_v + s * 128 + vc * 16);
+        uint8_t* dst = smem + kOffV + vc * kChunkStride64 + (s & 7) * 16 + (s >> 3) * kRowGroup;
+        if (s >= rows) q = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (kVExact) {
+          *reinterpret_cast<uint4*>(dst) = q;
+        } else {
+          float x[8];
+          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2<io_t>(words[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+          }
+          uint4 hi, lo;
+          split8(x, hi, lo);
+          *reinterpret_cast<uint4*>(dst) = hi;
+          *reinterpret_cast<uint4*>(dst + kTile64) = lo;
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= P = X1 X2^T ; Q = X1 S0 =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      issue_gemm(tmem + kColP, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
+                 sbase + kOffX2, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup, idesc_kk128, 4, false);
+      issue_gemm(tmem + kColQ, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
+                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, false);
+      mma_commit(bar_mma);
+    }
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+
+    // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
+    {
+      const int t = (quad & 1) * 32 + lane;  // chunk row of this thread
+      float vals[64];
+      {
+        uint32_t regs[32];
+        tmem_ld32(tmem_lane + kColP + half * 64, regs);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vals[i] = __uint_as_float(regs[i]);
+        tmem_ld32(tmem_lane + kColP + half * 64 + 32, regs);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vals[32 + i] = __uint_as_float(regs[i]);
+      }
+      const int limit = quad < 2 ? t : t + 1;  // keep columns s < limit
+#pragma unroll
+      for (int s = 0; s < 64; ++s)
+        if (s >= limit) vals[s] = 0.0f;
+      if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
+        float4* dst = reinterpret_cast<float4*>(smem + kOffAb + t * kInvLd * 4);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) dst[j] = make_float4(vals[4 * j], vals[4 * j + 1], vals[4 * j + 2], vals[4 * j + 3]);
+      } else {
+        // quad<2, half=1: A_ak -> X3 row t;   quad>=2, half=1: A_rk -> X3 row 64+t;
+        // quad>=2, half=0: A_rb -> X1 area (now [T; A_rb]) row 64+t
+        const int row = quad < 2 ? t : 64 + t;
+        uint8_t* dst = smem + (half == 1 ? kOffX3 : kOffX1) + (row >> 3) * kRowGroup + (row & 7) * 16;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 hi, lo;
+          split8(vals + 8 * j, hi, lo);
+          *reinterpret_cast<uint4*>(dst + j * kChunkStride128) = hi;
+          *reinterpret_cast<uint4*>(dst + kTile128 + j * kChunkStride128) = lo;
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      issue_gemm(tmem + kColQ, sbase + kOffX3, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
+                 sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, true);
+      mma_commit(bar_mma);
+    }
+    {
+      float* ab = reinterpret_cast<float*>(smem + kOffAb);
+      float* ti = reinterpret_cast<float*>(smem + kOffTi);
+      float* mb = reinterpret_cast<float*>(smem + kOffMb);
+      // step 1: the four 16x16 diagonal blocks by forward substitution, one column per thread
+      if (tid < 64) {
+        const int d = tid >> 4, j = tid & 15;
+        float x[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          float acc = t == j ? 1.0f : 0.0f;
+#pragma unroll
+          for (int s = 0; s < t; ++s) acc = fmaf(ab[(16 * d + t) * kInvLd + 16 * d + s], x[s], acc);
+          x[t] = acc;
+          ti[(16 * d + t) * kInvLd + 16 * d + j] = acc;
+        }
+      } else {  // zero the blocks above the diagonal
+        for (int e = tid - 64; e < 6 * 256; e += kThreads - 64) {
+          const int blk = e >> 8, rr = (e >> 4) & 15, cc = e & 15;
+          const int bi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+          const int bj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+          ti[(16 * bi + rr) * kInvLd + 16 * bj + cc] = 0.0f;
+        }
+      }
+      __syncthreads();
+      // step 2: blocks below the diagonal, one block diagonal at a time:
+      //   T_ij = D_i * sum_{m=j}^{i-1} A_im T_mj
+      const int rr = tid >> 4, cc = tid & 15;
+      for (int offd = 1; offd < 4; ++offd) {
+        for (int i = offd; i < 4; ++i) {
+          const int j = i - offd;
+          float acc = 0.0f;
+          for (int m = j; m < i; ++m) {
+#pragma unroll
+            for (int s = 0; s < 16; ++s)
+              acc = fmaf(ab[(16 * i + rr) * kInvLd + 16 * m + s], ti[(16 * m + s) * kInvLd + 16 * j + cc], acc);
+          }
+          mb[((i - offd) * 16 + rr) * 17 + cc] = acc;
+        }
+        __syncthreads();
+        for (int i = offd; i < 4; ++i) {
+          const int j = i - offd;
+          float acc = 0.0f;
+#pragma unroll
+          for (int s = 0; s < 16; ++s)
+            acc = fmaf(ti[(16 * i + rr) * kInvLd + 16 * i + s], mb[((i - offd) * 16 + s) * 17 + cc], acc);
+          ti[(16 * i + rr) * kInvLd + 16 * j + cc] = acc;
+        }
+        __syncthreads();
+      }
+      // step 3: T -> rows 0..63 of the X1 area (hi/lo, K-major)
+      {
+        const int t = tid >> 2, cg = tid & 3;
+        const float* src = ti + t * kInvLd + cg * 16;
+        uint8_t* dst = smem + kOffX1 + (t >> 3) * kRowGroup + (t & 7) * 16;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float x[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) x[e] = src[8 * j + e];
+          uint4 hi, lo;
+          split8(x, hi, lo);
+          *reinterpret_cast<uint4*>(dst + (cg * 2 + j) * kChunkStride128) = hi;
+          *reinterpret_cast<uint4*>(dst + kTile128 + (cg * 2 + j) * kChunkStride128) = lo;
+        }
+      }
+    }
+    // wait for Q, then W = Q[0..63] -> operand tile (rows = token, MN-major)
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+    auto rows_to_operand = [&](uint32_t col) {  // lanes 0..63 x 64 columns at `col` -> kOffOp (hi/lo)
+      if (quad < 2) {
+        const int t = quad * 32 + lane;
+        uint32_t regs[32];
+        tmem_ld32(tmem_lane + col + half * 32, regs);
+        tmem_ld_wait();
+        uint8_t* op = smem + kOffOp + (t & 7) * 16 + (t >> 3) * kRowGroup;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 hi, lo;
+          split8(reinterpret_cast<const float*>(regs) + 8 * j, hi, lo);
+          *reinterpret_cast<uint4*>(op + (half * 4 + j) * kChunkStride64) = hi;
+          *reinterpret_cast<uint4*>(op + kTile64 + (half * 4 + j) * kChunkStride64) = lo;
+        }
+      }
+    };
+    rows_to_operand(kColQ);
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= U = T W  (rows 64..127 of this product are unused) =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      if (c + 1 < n_chunks) issue_tma(c + 1);  // the staging area (and the inverse scratch in it) is free
+      issue_gemm(tmem + kColU, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
+                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, false);
+      mma_commit(bar_mma);
+    }
+    if (c + 1 < n_chunks) tma_in_flight = true;
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+    rows_to_operand(kColU);
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= Q[64..] += A_rb U ;  S += Bt^T U + Kt^T V =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      issue_gemm(tmem + kColQ, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
+                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, true);
+      // X2 read MN-major: M = key channel (16-byte chunks at kChunkStride128), contraction = tile row
+      issue_gemm(tmem + kColS, sbase + kOffX2, kTile128, 2 * kRowGroup, kRowGroup, kChunkStride128,
+                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_mnmn64, 4, true);
+      issue_gemm(tmem + kColS, sbase + kOffX2 + 8 * kRowGroup, kTile128, 2 * kRowGroup, kRowGroup, kChunkStride128,
+                 sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_mnmn64, 4, true);
+      mma_commit(bar_mma);
+    }
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+    if (quad >= 2) {
+      // ---- y rows: lanes 64..127 of Q ----
+      const int t = (quad - 2) * 32 + lane;
+      uint32_t regs[32];
+      tmem_ld32(tmem_lane + kColQ + half * 32, regs);
+      tmem_ld_wait();
+      if (t < rows) {
+        const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32;
+        float yv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) yv[i] = __uint_as_float(regs[i]) * p.scale;
+        io_t* yp = static_cast<io_t*>(p.y) + out;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          alignas(16) io_t packed[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) packed[e] = from_f32<io_t>(yv[8 * j + e]);
+          *reinterpret_cast<uint4*>(yp + 8 * j) = *reinterpret_cast<const uint4*>(packed);
+        }
+        if (p.y_f32 != nullptr) {
+          float4* yf = reinterpret_cast<float4*>(p.y_f32 + out);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) yf[j] = make_float4(yv[4 * j], yv[4 * j + 1], yv[4 * j + 2], yv[4 * j + 3]);
+        }
+      }
+    } else {
+      // ---- state rows: S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store at the end) ----
+      const int krow = quad * 32 + lane;
+      uint32_t regs[32];
+      tmem_ld32(tmem_lane + kColS + half * 32, regs);
+      tmem_ld_wait();
+      const float gl = gamma_l[krow];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) regs[i] = __float_as_uint(__uint_as_float(regs[i]) * gl);
+      if (c + 1 < n_chunks) {
+        tmem_st32(tmem_lane + kColS + half * 32, regs);
+        uint8_t* op = smem + kOffOp + (krow & 7) * 16 + (krow >> 3) * kRowGroup;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 hi, lo;
+          split8(reinterpret_cast<const float*>(regs) + 8 * j, hi, lo);
+          *reinterpret_cast<uint4*>(op + (half * 4 + j) * kChunkStride64) = hi;
+          *reinterpret_cast<uint4*>(op + kTile64 + (half * 4 + j) * kChunkStride64) = lo;
+        }
+        tmem_st_wait();
+      } else {
+        float4* dst = reinterpret_cast<float4*>(state_g + krow * kHeadDim + half * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          __stcs(dst + i, make_float4(__uint_as_float(regs[4 * i]), __uint_as_float(regs[4 * i + 1]),
+                                      __uint_as_float(regs[4 * i + 2]), __uint_as_float(regs[4 * i + 3])));
+      }
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+  }
+
+  if (failed) {
+    if (tid == 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 1);
+    if (tma_in_flight) mbar_wait(bar_tma, tma_parity, 200000u);  // bounded drain of the load in flight
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
+        query != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// [64, H, T] view of a packed [T, H, 64] 16-bit tensor; box = one head's 64 rows x 64 columns.
+int make_map(CUtensorMap* map, const void* base, int total_tokens, int heads, bool bf16) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(FRWKV_ERR_CUDA, "wkv7_prefill: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(total_tokens)};
+  const cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(heads) * 128};
+  const cuuint32_t box[3] = {64, 1, 64};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                         const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return fail(FRWKV_ERR_CUDA, "wkv7_prefill: cuTensorMapEncodeTiled failed (%d)", int(rc));
+  return FRWKV_OK;
+}
+
+template <typename io_t>
+int launch_typed(const ChunkParams& p, const Maps& maps, bool logits, cudaStream_t stream) {
+  auto kernel = logits ? wkv7_chunk_tc_kernel<io_t, true> : wkv7_chunk_tc_kernel<io_t, false>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return check_launch("wkv7_chunk_tc_kernel shared-memory attribute");
+  const long long ctas = static_cast<long long>(p.n_seq) * p.heads;
+  if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: too many (sequence, head) pairs");
+  kernel<<<static_cast<unsigned>(ctas), kThreads, kSmemBytes, stream>>>(p, maps);
+  return check_launch("wkv7_chunk_tc_kernel");
+}
+
+}  // namespace
+
+size_t chunk_tc_workspace_bytes(int, int, int) { return 0; }
+
+int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
+                    const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
+                    void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
+                    float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                    cudaStream_t stream) {
+  (void)max_seqlen;
+  (void)workspace;
+  (void)workspace_bytes;
+  const bool bf16 = io_dtype == FRWKV_IO_BF16;
+  Maps maps;
+  const void* srcs[6] = {r, w, k, v, a, b};
+  CUtensorMap* dsts[6] = {&maps.r, &maps.w, &maps.k, &maps.v, &maps.a, &maps.b};
+  for (int i = 0; i < 6; ++i) {
+    const int rc = make_map(dsts[i], srcs[i], total_tokens, heads, bf16);
+    if (rc != FRWKV_OK) return rc;
+  }
+  ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale};
+  const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
+  if (bf16) return launch_typed<__nv_bfloat16>(p, maps, logits, stream);
+  return launch_typed<__half>(p, maps, logits, stream);
+}
+
 }  // namespace frwkv
