@@ -18,7 +18,7 @@
 // enough, so each fp32 operand x is split into hi = bf16(x), lo = bf16(x - hi) and a product
 // is issued as hi*hi + hi*lo + lo*hi (about 16 significant bits); V is exact in bf16 and
 // needs no lo part.  The triangular inverse is computed in fp32 on CUDA cores (16x16
-// diagonal blocks by substitution, then block substitution).
+// diagonal blocks by substitution, merged to 32x32 and then 64x64 by block products).
 //
 // Data movement: the six token tiles of a chunk arrive by TMA (cp.async.bulk.tensor.3d over
 // the [64, H, T] view of each tensor) into one staging area; operands are written into
@@ -64,12 +64,26 @@ constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 128;  // + alignment sla
 constexpr int kInvLd = 68;                                      // padded row length (floats)
 constexpr uint32_t kOffAb = kOffRaw;                            // A_ab   [64][68]
 constexpr uint32_t kOffTi = kOffAb + 64 * kInvLd * 4;           // T      [64][68]
-constexpr uint32_t kOffMb = kOffTi + 64 * kInvLd * 4;           // block products [3][16][17]
-static_assert(kOffMb + 3 * 16 * 17 * 4 <= kOffX1, "inverse scratch must fit in the staging area");
+constexpr int kMbLd = 34;                                       // padded row length of the product scratch
+constexpr uint32_t kOffMb = kOffTi + 64 * kInvLd * 4;           // intermediate block product [32][34]
+static_assert(kOffMb + 32 * kMbLd * 4 <= kOffX1, "inverse scratch must fit in the staging area");
 
 // ---- TMEM map (columns) --------------------------------------------------------------------
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColP = 0, kColQ = 128, kColU = 192, kColS = 256;
+
+// Optional per-phase cycle counters of CTA 0 (development builds only).
+#ifdef FRWKV_CHUNK_TIMING
+__device__ long long g_phase_ticks[16];
+#define FRWKV_PHASE(i)                                        \
+  if (tid == 0 && blockIdx.x == 0) {                          \
+    const long long now = clock64();                          \
+    g_phase_ticks[i] += now - phase_t0;                       \
+    phase_t0 = now;                                           \
+  }
+#else
+#define FRWKV_PHASE(i)
+#endif
 
 struct ChunkParams {
   const int* cu;
@@ -87,6 +101,18 @@ struct ChunkParams {
 struct Maps {
   CUtensorMap r, w, k, v, a, b;
 };
+
+// SFU approximations (relative error about 2^-22, far below the bf16x2 operand precision)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_log2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo_elem, float hi_elem) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo_elem, hi_elem);
@@ -115,20 +141,30 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t packed) {
   return __half22float2(*reinterpret_cast<__half2*>(&packed));
 }
 
-// One dense contraction D (+)= A * B over `ksteps` steps of 16, as hi*hi (+ hi*lo) (+ lo*hi).
-// a_lo_off / b_lo_off: byte distance from the hi part to the lo part (0 = operand has no lo part).
-__device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_addr, uint32_t a_lo_off, uint32_t a_kstep,
-                                           uint32_t a_lbo, uint32_t a_sbo, uint32_t b_addr, uint32_t b_lo_off,
-                                           uint32_t b_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t idesc,
-                                           int ksteps, bool accumulate) {
-  bool acc = accumulate;
-  for (int ks = 0; ks < ksteps; ++ks) {
-    const uint64_t a_hi = smem_desc(a_addr + ks * a_kstep, a_lbo, a_sbo);
-    const uint64_t b_hi = smem_desc(b_addr + ks * b_kstep, b_lbo, b_sbo);
-    mma_f16_ss(tmem_d, a_hi, b_hi, idesc, acc);
-    acc = true;
-    if (b_lo_off != 0) mma_f16_ss(tmem_d, a_hi, smem_desc(b_addr + b_lo_off + ks * b_kstep, b_lbo, b_sbo), idesc, true);
-    if (a_lo_off != 0) mma_f16_ss(tmem_d, smem_desc(a_addr + a_lo_off + ks * a_kstep, a_lbo, a_sbo), b_hi, idesc, true);
+// One dense contraction D (+)= A * B over four steps of 16, as hi*hi (+ hi*lo) (+ lo*hi).
+// The descriptors of step 0 are built once per kernel; a step only advances the 14-bit
+// start-address field (units of 16 bytes), which cannot carry out of the low word.
+struct Operand {
+  uint64_t hi, lo;   // descriptors of the hi and lo parts at step 0 (lo == 0: no lo part)
+  uint32_t kstep16;  // start-address advance per step of 16, in 16-byte units
+};
+__device__ __forceinline__ Operand make_operand(uint32_t addr, uint32_t lo_off, uint32_t kstep, uint32_t lbo,
+                                                uint32_t sbo) {
+  Operand o;
+  o.hi = smem_desc(addr, lbo, sbo);
+  o.lo = lo_off != 0 ? smem_desc(addr + lo_off, lbo, sbo) : 0ull;
+  o.kstep16 = kstep >> 4;
+  return o;
+}
+template <bool A_LO, bool B_LO>
+__device__ __forceinline__ void issue_gemm(uint32_t tmem_d, const Operand& a, const Operand& b, uint32_t idesc,
+                                           bool accumulate) {
+#pragma unroll
+  for (uint32_t ks = 0; ks < 4; ++ks) {
+    const uint64_t a_hi = a.hi + ks * a.kstep16, b_hi = b.hi + ks * b.kstep16;
+    mma_f16_ss(tmem_d, a_hi, b_hi, idesc, accumulate || ks > 0);
+    if constexpr (B_LO) mma_f16_ss(tmem_d, a_hi, b.lo + ks * b.kstep16, idesc, true);
+    if constexpr (A_LO) mma_f16_ss(tmem_d, a.lo + ks * a.kstep16, b_hi, idesc, true);
   }
 }
 
@@ -231,8 +267,22 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   constexpr bool kVExact = std::is_same<io_t, __nv_bfloat16>::value;
   constexpr uint32_t v_lo_off = kVExact ? 0u : kTile64;
 
+  // operand descriptors (fixed for the whole kernel)
+  const Operand op_x1 = make_operand(sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup);
+  const Operand op_x2 = make_operand(sbase + kOffX2, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup);
+  const Operand op_x3 = make_operand(sbase + kOffX3, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup);
+  const Operand op_rows = make_operand(sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64);
+  const Operand op_v = make_operand(sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kChunkStride64);
+  // [Bt; Kt] read MN-major: M = key channel (16-byte chunks at kChunkStride128), contraction = tile row
+  const Operand op_bt = make_operand(sbase + kOffX2, kTile128, 2 * kRowGroup, kRowGroup, kChunkStride128);
+  const Operand op_kt = make_operand(sbase + kOffX2 + 8 * kRowGroup, kTile128, 2 * kRowGroup, kRowGroup,
+                                     kChunkStride128);
+
   uint32_t mma_uses = 0;
   bool failed = false;
+#ifdef FRWKV_CHUNK_TIMING
+  long long phase_t0 = clock64();
+#endif
   const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
 
   for (int c = 0; c < n_chunks; ++c) {
@@ -246,6 +296,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       tma_in_flight = false;
       tma_parity ^= 1u;
     }
+    FRWKV_PHASE(0)
     {
       const int kp = lane;       // key channels 2*kp, 2*kp+1
       const int tg = warp;       // rows 8*tg .. 8*tg+7
@@ -265,11 +316,11 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         const float2 w2 = unpack2<io_t>(raw_w[t * 32 + kp]);
         float2 l;
         if constexpr (LOGITS) {
-          l.x = -kRateLog2e / (1.0f + exp2f(-kLog2e * (w2.x + bias2.x)));
-          l.y = -kRateLog2e / (1.0f + exp2f(-kLog2e * (w2.y + bias2.y)));
+          l.x = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.x + bias2.x)));
+          l.y = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.y + bias2.y)));
         } else {
-          l.x = log2f(w2.x);
-          l.y = log2f(w2.y);
+          l.x = fast_log2(w2.x);
+          l.y = fast_log2(w2.y);
         }
         if (t >= rows) l = make_float2(0.f, 0.f);
         lw[i] = l;
@@ -285,6 +336,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         off.x += s.x;
         off.y += s.y;
       }
+      float2 g_prev = make_float2(fast_exp2(off.x), fast_exp2(off.y));
       uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kChunkStride128 + (kp & 3) * 4;
       uint8_t* x2 = smem + kOffX2 + (kp >> 2) * kChunkStride128 + (kp & 3) * 4;
 #pragma unroll
@@ -292,9 +344,10 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         const int t = tg * 8 + i;
         const bool live = t < rows;
         const float2 lg = make_float2(off.x + cum[i].x, off.y + cum[i].y);
-        const float2 g = make_float2(exp2f(lg.x), exp2f(lg.y));
-        const float2 gi = make_float2(exp2f(-lg.x), exp2f(-lg.y));
-        const float2 gx = make_float2(exp2f(lg.x - lw[i].x), exp2f(lg.y - lw[i].y));
+        const float2 g = make_float2(fast_exp2(lg.x), fast_exp2(lg.y));
+        const float2 gi = make_float2(fast_exp2(-lg.x), fast_exp2(-lg.y));
+        const float2 gx = g_prev;  // exclusive product = inclusive product of the previous row
+        g_prev = g;
         float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
         float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
         float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
@@ -354,13 +407,12 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(1)
     // ================= P = X1 X2^T ; Q = X1 S0 =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
-      issue_gemm(tmem + kColP, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
-                 sbase + kOffX2, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup, idesc_kk128, 4, false);
-      issue_gemm(tmem + kColQ, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
-                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, false);
+      issue_gemm<true, true>(tmem + kColP, op_x1, op_x2, idesc_kk128, false);
+      issue_gemm<true, true>(tmem + kColQ, op_x1, op_rows, idesc_kmn64, false);
       mma_commit(bar_mma);
     }
     {
@@ -370,6 +422,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       tcgen05_fence_after_sync();
     }
 
+    FRWKV_PHASE(2)
     // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
     {
       const int t = (quad & 1) * 32 + lane;  // chunk row of this thread
@@ -411,63 +464,127 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(3)
     // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
-      issue_gemm(tmem + kColQ, sbase + kOffX3, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
-                 sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, true);
+      issue_gemm<true, !kVExact>(tmem + kColQ, op_x3, op_v, idesc_kmn64, true);
       mma_commit(bar_mma);
     }
     {
       float* ab = reinterpret_cast<float*>(smem + kOffAb);
       float* ti = reinterpret_cast<float*>(smem + kOffTi);
       float* mb = reinterpret_cast<float*>(smem + kOffMb);
-      // step 1: the four 16x16 diagonal blocks by forward substitution, one column per thread
+      // level 0: the four 16x16 diagonal blocks by forward substitution, one column per thread
       if (tid < 64) {
         const int d = tid >> 4, j = tid & 15;
+        const float* blk = ab + (16 * d) * kInvLd + 16 * d;
         float x[16];
 #pragma unroll
         for (int t = 0; t < 16; ++t) {
-          float acc = t == j ? 1.0f : 0.0f;
+          float row[16];
 #pragma unroll
-          for (int s = 0; s < t; ++s) acc = fmaf(ab[(16 * d + t) * kInvLd + 16 * d + s], x[s], acc);
-          x[t] = acc;
-          ti[(16 * d + t) * kInvLd + 16 * d + j] = acc;
+          for (int q4 = 0; q4 < (t + 3) / 4; ++q4) {
+            const float4 f = *reinterpret_cast<const float4*>(blk + t * kInvLd + 4 * q4);
+            row[4 * q4] = f.x; row[4 * q4 + 1] = f.y; row[4 * q4 + 2] = f.z; row[4 * q4 + 3] = f.w;
+          }
+          float acc0 = t == j ? 1.0f : 0.0f, acc1 = 0.0f;
+#pragma unroll
+          for (int s2 = 0; s2 < t; ++s2) {
+            if (s2 & 1) acc1 = fmaf(row[s2], x[s2], acc1);
+            else acc0 = fmaf(row[s2], x[s2], acc0);
+          }
+          x[t] = acc0 + acc1;
+          ti[(16 * d + t) * kInvLd + 16 * d + j] = x[t];
         }
-      } else {  // zero the blocks above the diagonal
-        for (int e = tid - 64; e < 6 * 256; e += kThreads - 64) {
-          const int blk = e >> 8, rr = (e >> 4) & 15, cc = e & 15;
-          const int bi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
-          const int bj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
-          ti[(16 * bi + rr) * kInvLd + 16 * bj + cc] = 0.0f;
+      } else {  // zero everything above the block diagonal: 16-blocks (0,1), (2,3) and the 32-block (0,1)
+        for (int e = tid - 64; e < 512 + 1024; e += kThreads - 64) {
+          int rr, cc;
+          if (e < 512) {
+            const int blk = e >> 8;
+            rr = 32 * blk + ((e >> 4) & 15);
+            cc = 32 * blk + 16 + (e & 15);
+          } else {
+            rr = (e - 512) >> 5;
+            cc = 32 + ((e - 512) & 31);
+          }
+          ti[rr * kInvLd + cc] = 0.0f;
         }
       }
       __syncthreads();
-      // step 2: blocks below the diagonal, one block diagonal at a time:
-      //   T_ij = D_i * sum_{m=j}^{i-1} A_im T_mj
-      const int rr = tid >> 4, cc = tid & 15;
-      for (int offd = 1; offd < 4; ++offd) {
-        for (int i = offd; i < 4; ++i) {
-          const int j = i - offd;
-          float acc = 0.0f;
-          for (int m = j; m < i; ++m) {
+      // level 1: the two 32x32 diagonal blocks: T[hi,lo] = D_hi * (A[hi,lo] * D_lo), 16x16 each
+      {
+        const int b = tid >> 7, rr = (tid >> 3) & 15, c0 = (tid & 7) * 2;
+        const int lo = 32 * b, hi = 32 * b + 16;
+        float acc[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int s = 0; s < 16; ++s)
-              acc = fmaf(ab[(16 * i + rr) * kInvLd + 16 * m + s], ti[(16 * m + s) * kInvLd + 16 * j + cc], acc);
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const float4 av = *reinterpret_cast<const float4*>(ab + (hi + rr) * kInvLd + lo + 4 * s4);
+          const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 tv = *reinterpret_cast<const float2*>(ti + (lo + 4 * s4 + e) * kInvLd + lo + c0);
+            acc[0] = fmaf(a4[e], tv.x, acc[0]);
+            acc[1] = fmaf(a4[e], tv.y, acc[1]);
           }
-          mb[((i - offd) * 16 + rr) * 17 + cc] = acc;
         }
+        *reinterpret_cast<float2*>(mb + (b * 16 + rr) * kMbLd + c0) = make_float2(acc[0], acc[1]);
         __syncthreads();
-        for (int i = offd; i < 4; ++i) {
-          const int j = i - offd;
-          float acc = 0.0f;
+        acc[0] = acc[1] = 0.0f;
 #pragma unroll
-          for (int s = 0; s < 16; ++s)
-            acc = fmaf(ti[(16 * i + rr) * kInvLd + 16 * i + s], mb[((i - offd) * 16 + s) * 17 + cc], acc);
-          ti[(16 * i + rr) * kInvLd + 16 * j + cc] = acc;
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const float4 dv = *reinterpret_cast<const float4*>(ti + (hi + rr) * kInvLd + hi + 4 * s4);
+          const float d4[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 xv = *reinterpret_cast<const float2*>(mb + (b * 16 + 4 * s4 + e) * kMbLd + c0);
+            acc[0] = fmaf(d4[e], xv.x, acc[0]);
+            acc[1] = fmaf(d4[e], xv.y, acc[1]);
+          }
         }
-        __syncthreads();
+        *reinterpret_cast<float2*>(ti + (hi + rr) * kInvLd + lo + c0) = make_float2(acc[0], acc[1]);
       }
+      __syncthreads();
+      // level 2: T[32..63, 0..31] = T_hi * (A[32..63, 0..31] * T_lo), 32x32, a 2x2 tile per thread
+      {
+        const int r0 = (tid >> 4) * 2, c0 = (tid & 15) * 2;
+        float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+#pragma unroll
+        for (int s4 = 0; s4 < 8; ++s4) {
+          const float4 a0 = *reinterpret_cast<const float4*>(ab + (32 + r0) * kInvLd + 4 * s4);
+          const float4 a1 = *reinterpret_cast<const float4*>(ab + (33 + r0) * kInvLd + 4 * s4);
+          const float a0v[4] = {a0.x, a0.y, a0.z, a0.w}, a1v[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 tv = *reinterpret_cast<const float2*>(ti + (4 * s4 + e) * kInvLd + c0);
+            acc[0][0] = fmaf(a0v[e], tv.x, acc[0][0]);
+            acc[0][1] = fmaf(a0v[e], tv.y, acc[0][1]);
+            acc[1][0] = fmaf(a1v[e], tv.x, acc[1][0]);
+            acc[1][1] = fmaf(a1v[e], tv.y, acc[1][1]);
+          }
+        }
+        *reinterpret_cast<float2*>(mb + r0 * kMbLd + c0) = make_float2(acc[0][0], acc[0][1]);
+        *reinterpret_cast<float2*>(mb + (r0 + 1) * kMbLd + c0) = make_float2(acc[1][0], acc[1][1]);
+        __syncthreads();
+        acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.0f;
+#pragma unroll
+        for (int s4 = 0; s4 < 8; ++s4) {
+          const float4 d0 = *reinterpret_cast<const float4*>(ti + (32 + r0) * kInvLd + 32 + 4 * s4);
+          const float4 d1 = *reinterpret_cast<const float4*>(ti + (33 + r0) * kInvLd + 32 + 4 * s4);
+          const float d0v[4] = {d0.x, d0.y, d0.z, d0.w}, d1v[4] = {d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 xv = *reinterpret_cast<const float2*>(mb + (4 * s4 + e) * kMbLd + c0);
+            acc[0][0] = fmaf(d0v[e], xv.x, acc[0][0]);
+            acc[0][1] = fmaf(d0v[e], xv.y, acc[0][1]);
+            acc[1][0] = fmaf(d1v[e], xv.x, acc[1][0]);
+            acc[1][1] = fmaf(d1v[e], xv.y, acc[1][1]);
+          }
+        }
+        *reinterpret_cast<float2*>(ti + (32 + r0) * kInvLd + c0) = make_float2(acc[0][0], acc[0][1]);
+        *reinterpret_cast<float2*>(ti + (33 + r0) * kInvLd + c0) = make_float2(acc[1][0], acc[1][1]);
+      }
+      __syncthreads();
       // step 3: T -> rows 0..63 of the X1 area (hi/lo, K-major)
       {
         const int t = tid >> 2, cg = tid & 3;
@@ -485,6 +602,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         }
       }
     }
+    FRWKV_PHASE(4)
     // wait for Q, then W = Q[0..63] -> operand tile (rows = token, MN-major)
     {
       const bool ok = mbar_wait(bar_mma, mma_uses & 1);
@@ -513,12 +631,12 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(5)
     // ================= U = T W  (rows 64..127 of this product are unused) =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
       if (c + 1 < n_chunks) issue_tma(c + 1);  // the staging area (and the inverse scratch in it) is free
-      issue_gemm(tmem + kColU, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
-                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, false);
+      issue_gemm<true, true>(tmem + kColU, op_x1, op_rows, idesc_kmn64, false);
       mma_commit(bar_mma);
     }
     if (c + 1 < n_chunks) tma_in_flight = true;
@@ -528,21 +646,19 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (__syncthreads_or(!ok)) { failed = true; break; }
       tcgen05_fence_after_sync();
     }
+    FRWKV_PHASE(6)
     rows_to_operand(kColU);
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(7)
     // ================= Q[64..] += A_rb U ;  S += Bt^T U + Kt^T V =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
-      issue_gemm(tmem + kColQ, sbase + kOffX1, kTile128, 2 * kChunkStride128, kChunkStride128, kRowGroup,
-                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_kmn64, 4, true);
-      // X2 read MN-major: M = key channel (16-byte chunks at kChunkStride128), contraction = tile row
-      issue_gemm(tmem + kColS, sbase + kOffX2, kTile128, 2 * kRowGroup, kRowGroup, kChunkStride128,
-                 sbase + kOffOp, kTile64, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_mnmn64, 4, true);
-      issue_gemm(tmem + kColS, sbase + kOffX2 + 8 * kRowGroup, kTile128, 2 * kRowGroup, kRowGroup, kChunkStride128,
-                 sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kChunkStride64, idesc_mnmn64, 4, true);
+      issue_gemm<true, true>(tmem + kColQ, op_x1, op_rows, idesc_kmn64, true);
+      issue_gemm<true, true>(tmem + kColS, op_bt, op_rows, idesc_mnmn64, true);
+      issue_gemm<true, !kVExact>(tmem + kColS, op_kt, op_v, idesc_mnmn64, true);
       mma_commit(bar_mma);
     }
     {
@@ -551,6 +667,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (__syncthreads_or(!ok)) { failed = true; break; }
       tcgen05_fence_after_sync();
     }
+    FRWKV_PHASE(8)
     if (quad >= 2) {
       // ---- y rows: lanes 64..127 of Q ----
       const int t = (quad - 2) * 32 + lane;
@@ -608,6 +725,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
     tcgen05_fence_after_sync();
+    FRWKV_PHASE(9)
   }
 
   if (failed) {
