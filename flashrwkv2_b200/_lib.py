@@ -14,12 +14,14 @@ IO_BF16, IO_FP16, IO_FP32 = 0, 1, 2
 DECAY_LOGITS, DECAY_RETENTION = 0, 1
 PREFILL_AUTO, PREFILL_RECURRENT, PREFILL_CHUNK_TC = 0, 1, 2
 ABI_VERSION = 1
+STATIC_POOL_SLOTS = 65536
 
 # every symbol include/frwkv_sm100.h declares
 SYMBOLS = (
     "frwkv_sm100_abi_version",
     "frwkv_sm100_last_error",
     "frwkv_sm100_wkv7_validate_metadata",
+    "frwkv_sm100_wkv7_validate_metadata_static",
     "frwkv_sm100_wkv7_recurrent",
     "frwkv_sm100_wkv7_prefill",
     "frwkv_sm100_wkv7_prefill_workspace_bytes",
@@ -48,6 +50,8 @@ def load() -> ctypes.CDLL:
     lib.frwkv_sm100_last_error.argtypes = []
     lib.frwkv_sm100_wkv7_validate_metadata.restype = ci
     lib.frwkv_sm100_wkv7_validate_metadata.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp]
+    lib.frwkv_sm100_wkv7_validate_metadata_static.restype = ci
+    lib.frwkv_sm100_wkv7_validate_metadata_static.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]
     lib.frwkv_sm100_wkv7_recurrent.restype = ci
     lib.frwkv_sm100_wkv7_recurrent.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, vp]
     lib.frwkv_sm100_wkv7_prefill.restype = ci

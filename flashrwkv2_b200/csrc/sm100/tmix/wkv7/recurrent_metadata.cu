@@ -94,3 +94,62 @@ extern "C" int frwkv_sm100_wkv7_validate_metadata(
       n_active_sequences, status, seen_slots, cu_snapshot, slots_snapshot);
   return check_launch("validate_metadata");
 }
+
+// ---- the same validation with built-in scratch: nothing is allocated by anyone ----------------
+//
+// Some hosts that bind this library have no way to hand over device scratch: a foreign-language
+// runtime that wraps only the launch calls and owns no device allocator, or a serving loop that
+// must not call cudaMalloc on its hot path because that call can synchronise the whole device.
+// For them the duplicate-slot scratch lives in this module's own global memory: a fixed array
+// that every GPU loading the library keeps until the process exits (256 KiB).
+namespace frwkv {
+namespace {
+
+constexpr int kStaticSeenSlots = FRWKV_SM100_STATIC_POOL_SLOTS;
+static __device__ __align__(256) int g_static_seen_slots[kStaticSeenSlots];
+
+constexpr int kMaxDevices = 64;
+int* g_static_seen_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device
+
+// In host code the array's name is only a handle; the device address must be asked for, once per
+// device and with that device current.
+int static_scratch(int** out) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "validate_metadata_static: cudaGetDevice: %s", cudaGetErrorString(err));
+  if (device < 0 || device >= kMaxDevices)
+    return fail(FRWKV_ERR_UNSUPPORTED, "validate_metadata_static: device index %d out of range", device);
+  if (g_static_seen_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_static_seen_slots);
+    if (err != cudaSuccess || ptr == nullptr)
+      return fail(FRWKV_ERR_CUDA, "validate_metadata_static: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+    g_static_seen_ptr[device] = static_cast<int*>(ptr);
+  }
+  *out = g_static_seen_ptr[device];
+  return FRWKV_OK;
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_sm100_wkv7_validate_metadata_static(
+    const int32_t* cu_seqlens, const int32_t* slots, int n_seq_capacity, int token_capacity,
+    int pool_size, int max_seqlen, const int32_t* n_active_tokens,
+    const int32_t* n_active_sequences, int32_t* status, int32_t* cu_snapshot,
+    int32_t* slots_snapshot, void* stream) {
+  using namespace frwkv;
+  if (pool_size > kStaticSeenSlots)
+    return fail(FRWKV_ERR_UNSUPPORTED,
+                "validate_metadata_static: state pool of %d slots exceeds the built-in scratch of %d slots; "
+                "use frwkv_sm100_wkv7_validate_metadata with caller-provided scratch",
+                pool_size, kStaticSeenSlots);
+  int* seen = nullptr;
+  const int rc = static_scratch(&seen);
+  if (rc != FRWKV_OK) return rc;
+  // the kernel itself resets the first pool_size entries to "unseen" before using them, so
+  // whatever the previous call left behind cannot leak into this one
+  return frwkv_sm100_wkv7_validate_metadata(cu_seqlens, slots, n_seq_capacity, token_capacity, pool_size,
+                                            max_seqlen, n_active_tokens, n_active_sequences, status, seen,
+                                            cu_snapshot, slots_snapshot, stream);
+}

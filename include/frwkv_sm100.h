@@ -74,6 +74,25 @@ int frwkv_sm100_wkv7_validate_metadata(
     const int32_t* n_active_sequences, int32_t* status, int32_t* seen_slots,
     int32_t* cu_snapshot, int32_t* slots_snapshot, void* stream);
 
+/* The same validation for hosts that cannot provide device scratch (a binding from another
+ * language that owns no device allocator; a serving loop where cudaMalloc is off limits because
+ * it may synchronise the device).  No counterpart in the reference.  The duplicate-slot scratch
+ * is a fixed array inside the library (FRWKV_SM100_STATIC_POOL_SLOTS int32, 256 KiB, held by
+ * every GPU that loads the library until the process exits), so the call takes no seen_slots
+ * and neither it nor anything it calls allocates or frees memory.
+ *   - pool_size above FRWKV_SM100_STATIC_POOL_SLOTS is rejected (FRWKV_ERR_UNSUPPORTED);
+ *   - the first call on each device looks up the array's device address (a cheap runtime
+ *     query made with that device current); make that first call outside any stream capture;
+ *   - all calls on a device share the one array: the kernel re-initialises the part it uses
+ *     at the start of every call, but two such calls that overlap in time on the GPU
+ *     (different streams) would race, so keep them on one stream or otherwise ordered. */
+#define FRWKV_SM100_STATIC_POOL_SLOTS 65536
+int frwkv_sm100_wkv7_validate_metadata_static(
+    const int32_t* cu_seqlens, const int32_t* slots, int n_seq_capacity, int token_capacity,
+    int pool_size, int max_seqlen, const int32_t* n_active_tokens,
+    const int32_t* n_active_sequences, int32_t* status, int32_t* cu_snapshot,
+    int32_t* slots_snapshot, void* stream);
+
 /* Register-streaming recurrence (decode and short rows); stands in for
  * tmix_wkv7_recurrent_fp32_from_decay_logits_cuda and the kernels it selects
  * (csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.cu:90-281,457-517).
