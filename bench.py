@@ -46,8 +46,9 @@ ALGO_BYTES_PREFILL_TOKEN_HEAD = 7 * 128
 ALGO_BYTES_PREFILL_PAIR = 32768
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel at the headline
-# workload, from the ncu capture summarised under profiles/ (None until captured)
-DECODE_TRAFFIC_BYTES = None
+# workload (N=256, H=32), from the ncu capture summarised in profiles/decode_c1_wkv7_recurrent_stream_kernel.md.
+# It is below the algorithmic bytes because part of the written state is still dirty in L2 when the kernel ends.
+DECODE_TRAFFIC_BYTES = 140538368 + 77164544
 
 
 def load_peaks():
@@ -254,7 +255,7 @@ def run_ours(args, rank, local_rank, world):
 
     achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": DECODE_TRAFFIC_BYTES if is_decode else None,
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": DECODE_TRAFFIC_BYTES if name == "c1" else None,
                 "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo_bytes,
                 "kernel": "wkv7_recurrent_stream_kernel" if is_decode else "wkv7 prefill"}
     if not is_decode:
