@@ -1,0 +1,563 @@
+// WKV7 chunked prefill on tcgen05 tensor cores, 32-row chunks, two CTAs resident per SM.
+//
+// Same algebra, precision scheme and data movement as the 64-row kernel in chunk_tc.cu (see the
+// header there); what changes is the footprint.  With 32-row chunks the stacked operands
+// [At; Rt], [Bt; Kt], [A_ak; A_rk] and [T; A_rb] have 64 rows, so every product is a natural
+// M=64 MMA (no padding rows), one CTA needs 94 KB of shared memory and 256 TMEM columns, and
+// two CTAs of 256 threads (<= 128 registers) share an SM: while one waits for its MMAs or a
+// barrier the other one's CUDA-core phases run.  A 64-row accumulator of an M=64 MMA puts row i
+// in TMEM lane 32*(i/16) + i%16, i.e. every warp quadrant holds 16 rows in its lanes 0..15.
+//
+// Per chunk of L <= 32 rows (g_t = inclusive cumulative retention inside the chunk):
+//     P  = [At; Rt] [Bt; Kt]^T  (64x64) -> A_ab, A_ak (strictly lower), A_rb, A_rk (lower), 32x32 each
+//     Q  = [At; Rt] S0 + [A_ak; A_rk] V      (rows 0..31 = W, rows 32..63 = part of Y)
+//     U  = (I - A_ab)^-1 W ;  Y = scale (Q[32..] + A_rb U) ;  S <- diag(g_L)(S0 + Bt^T U + Kt^T V)
+#include "chunk_common.cuh"
+
+namespace frwkv {
+namespace {
+
+using namespace tc;
+using namespace chunk;
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kChunk = 32;
+
+// ---- shared-memory map (bytes) -------------------------------------------------------------
+constexpr uint32_t kStride64 = 8 * 128 + 16;  // stride between 16-byte chunks of a 64-row tile (padded)
+constexpr uint32_t kTileK64 = 8 * kStride64;  // 64 rows x 64 columns, one bf16 part: 8320
+constexpr uint32_t kTileK32 = 4 * kStride64;  // 64 rows x 32 columns, one bf16 part: 4160
+constexpr uint32_t kStride32 = 4 * 128 + 16;  // stride between 16-byte chunks of a 32-row tile (padded)
+constexpr uint32_t kTileV = 8 * kStride32;    // 32 rows x 64 columns, one bf16 part: 4224
+
+constexpr uint32_t kRawTile = kChunk * 128;           // one [32][64] 16-bit tile as TMA writes it
+constexpr uint32_t kOffRaw = 0;                       // r, w, k, v, a, b
+constexpr uint32_t kOffX1 = kOffRaw + 6 * kRawTile;   // [At; Rt] hi, lo (64 x 64)
+constexpr uint32_t kOffX2 = kOffX1 + 2 * kTileK64;    // [Bt; Kt] hi, lo (64 x 64)
+constexpr uint32_t kOffX3 = kOffX2 + 2 * kTileK64;    // [A_ak; A_rk] hi, lo (64 x 32)
+constexpr uint32_t kOffX4 = kOffX3 + 2 * kTileK32;    // [T; A_rb] hi, lo (64 x 32)
+constexpr uint32_t kOffOp = kOffX4 + 2 * kTileK32;    // S0 (64 rows) / W / U (32 rows) operand hi, lo
+constexpr uint32_t kOffV = kOffOp + 2 * kTileK64;     // V operand hi, lo (32 rows x 64)
+constexpr uint32_t kOffMisc = kOffV + 2 * kTileV;     // gamma_L[64], group sums [8][64], barriers
+constexpr uint32_t kMiscBytes = 64 * 4 + kWarps * 64 * 4 + 64;
+constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 128;
+static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM's shared memory");
+// fp32 scratch of the 32x32 inverse, aliased onto the TMA staging area (free after stage A)
+constexpr int kInvLd = 36;
+constexpr uint32_t kOffAb = kOffRaw;                   // A_ab [32][36]
+constexpr uint32_t kOffTi = kOffAb + 32 * kInvLd * 4;  // T    [32][36]
+constexpr int kMbLd = 17;
+constexpr uint32_t kOffMb = kOffTi + 32 * kInvLd * 4;  // block product [16][17]
+static_assert(kOffMb + 16 * kMbLd * 4 <= kOffX1, "inverse scratch must fit in the staging area");
+
+// ---- TMEM map (columns) --------------------------------------------------------------------
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColP = 0, kColQ = 64, kColU = 128, kColS = 192;
+
+template <typename io_t, bool LOGITS>
+__global__ void __launch_bounds__(kThreads, 2)
+wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3;       // TMEM lane quadrant this warp may access
+  const int half = warp >> 2;      // which 32 of an accumulator's 64 columns this warp handles
+  const bool row_lane = lane < 16; // lanes 0..15 of a quadrant hold accumulator rows 16*quad + lane
+  const int arow = quad * 16 + (lane & 15);
+
+  if (p.status != nullptr && p.status[0] != 0) {
+    fill_output_nan(static_cast<io_t*>(p.y), p.y_f32, static_cast<long long>(p.total_tokens) * p.heads * kHeadDim,
+                    static_cast<long long>(blockIdx.x) * kThreads + tid, static_cast<long long>(gridDim.x) * kThreads);
+    return;
+  }
+  const int active = p.status != nullptr ? p.status[2] : p.n_seq;
+  const int seq = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
+  if (seq >= active || seq >= p.n_seq) return;
+  const int t_begin = p.cu[seq], len = p.cu[seq + 1] - t_begin;
+  if (len <= 0) return;
+  const int n_chunks = (len + kChunk - 1) / kChunk;
+  const int slot = p.slots[seq];
+
+  float* gamma_l = reinterpret_cast<float*>(smem + kOffMisc);
+  float* group_sum = gamma_l + 64;  // [8][64] log2-decay sums of each 4-row group
+  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_sum + kWarps * 64);
+  uint64_t* bar_mma = bar_tma + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
+  const uint32_t sbase = smem_u32(smem);
+
+  if (tid == 0) {
+    mbar_init(bar_tma, 1);
+    mbar_init(bar_mma, 1);
+    mbar_fence_init();
+    tma_prefetch_descriptor(&maps.r);
+    tma_prefetch_descriptor(&maps.w);
+    tma_prefetch_descriptor(&maps.k);
+    tma_prefetch_descriptor(&maps.v);
+    tma_prefetch_descriptor(&maps.a);
+    tma_prefetch_descriptor(&maps.b);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+
+  auto issue_tma = [&](int chunk_index) {  // thread 0 only
+    const int row = t_begin + chunk_index * kChunk;
+    mbar_expect_tx(bar_tma, 6 * kRawTile);
+    tma_load_3d(smem + kOffRaw + 0 * kRawTile, &maps.r, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 1 * kRawTile, &maps.w, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 2 * kRawTile, &maps.k, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 3 * kRawTile, &maps.v, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 4 * kRawTile, &maps.a, bar_tma, 0, head, row);
+    tma_load_3d(smem + kOffRaw + 5 * kRawTile, &maps.b, bar_tma, 0, head, row);
+  };
+  if (tid == 0) issue_tma(0);
+  bool tma_in_flight = true;
+  uint32_t tma_parity = 0;
+
+  // 32 fp32 values (columns 32*half ..) of accumulator row `row` -> four 16-byte column chunks of the
+  // row-operand tile (hi/lo, rows = contraction index, MN-major)
+  auto store_operand_row = [&](int row, const uint32_t (&regs)[32]) {
+    uint8_t* op = smem + kOffOp + (row & 7) * 16 + (row >> 3) * kRowGroup;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 hi, lo;
+      split8(reinterpret_cast<const float*>(regs) + 8 * j, hi, lo);
+      *reinterpret_cast<uint4*>(op + (half * 4 + j) * kStride64) = hi;
+      *reinterpret_cast<uint4*>(op + kTileK64 + (half * 4 + j) * kStride64) = lo;
+    }
+  };
+
+  // ---- initial state: global -> TMEM (fp32) and -> S0 operand tile ----------------------------
+  float* state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
+  {
+    uint32_t regs[32];
+    if (row_lane) {
+      const float4* src = reinterpret_cast<const float4*>(state_g + arow * kHeadDim + half * 32);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 f = __ldcs(src + i);
+        regs[4 * i] = __float_as_uint(f.x);
+        regs[4 * i + 1] = __float_as_uint(f.y);
+        regs[4 * i + 2] = __float_as_uint(f.z);
+        regs[4 * i + 3] = __float_as_uint(f.w);
+      }
+      store_operand_row(arow, regs);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) regs[i] = 0u;
+    }
+    tmem_st32(tmem_lane + kColS + half * 32, regs);
+    tmem_st_wait();
+  }
+
+  constexpr uint32_t idesc_kk = instr_desc_f16(64, 64, kMajorK, kMajorK);
+  constexpr uint32_t idesc_kmn = instr_desc_f16(64, 64, kMajorK, kMajorMN);
+  constexpr uint32_t idesc_mnmn = instr_desc_f16(64, 64, kMajorMN, kMajorMN);
+  constexpr bool kVExact = std::is_same<io_t, __nv_bfloat16>::value;
+  constexpr uint32_t v_lo_off = kVExact ? 0u : kTileV;
+
+  // operand descriptors (fixed for the whole kernel); K-major tiles: chunk stride kStride64, row groups 128 B
+  const Operand op_x1 = make_operand(sbase + kOffX1, kTileK64, 2 * kStride64, kStride64, kRowGroup);
+  const Operand op_x2 = make_operand(sbase + kOffX2, kTileK64, 2 * kStride64, kStride64, kRowGroup);
+  const Operand op_x3 = make_operand(sbase + kOffX3, kTileK32, 2 * kStride64, kStride64, kRowGroup);
+  const Operand op_x4 = make_operand(sbase + kOffX4, kTileK32, 2 * kStride64, kStride64, kRowGroup);
+  // MN-major tiles (rows = contraction index): row groups 128 B apart, 16-byte column chunks at the tile's stride
+  const Operand op_rows = make_operand(sbase + kOffOp, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
+  const Operand op_v = make_operand(sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kStride32);
+  // [Bt; Kt] read MN-major: M = key channel, contraction = tile row (Bt rows 0..31, Kt rows 32..63)
+  const Operand op_bt = make_operand(sbase + kOffX2, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
+  const Operand op_kt = make_operand(sbase + kOffX2 + 4 * kRowGroup, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
+
+  uint32_t mma_uses = 0;
+  bool failed = false;
+  const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
+
+  for (int c = 0; c < n_chunks; ++c) {
+    const int rows = min(kChunk, len - c * kChunk);
+    const int row0 = t_begin + c * kChunk;
+
+    // ================= stage A: decay products and scaled operands =================
+    {
+      const bool ok = mbar_wait(bar_tma, tma_parity);
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tma_in_flight = false;
+      tma_parity ^= 1u;
+    }
+    {
+      constexpr int kRowsPerWarp = kChunk / kWarps;  // 4
+      const int kp = lane;                           // key channels 2*kp, 2*kp+1
+      const int tg = warp;                           // rows 4*tg .. 4*tg+3
+      const uint32_t* raw_r = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 0 * kRawTile);
+      const uint32_t* raw_w = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 1 * kRawTile);
+      const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
+      const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
+      const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
+      float2 bias2 = make_float2(0.f, 0.f);
+      if (bias_g != nullptr) bias2 = make_float2(to_f32(bias_g[2 * kp]), to_f32(bias_g[2 * kp + 1]));
+      float2 run = make_float2(0.f, 0.f);
+      float2 cum[kRowsPerWarp];
+#pragma unroll
+      for (int i = 0; i < kRowsPerWarp; ++i) {
+        const int t = tg * kRowsPerWarp + i;
+        const float2 w2 = unpack2<io_t>(raw_w[t * 32 + kp]);
+        float2 l;
+        if constexpr (LOGITS) {
+          l.x = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.x + bias2.x)));
+          l.y = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.y + bias2.y)));
+        } else {
+          l.x = fast_log2(w2.x);
+          l.y = fast_log2(w2.y);
+        }
+        if (t >= rows) l = make_float2(0.f, 0.f);
+        run.x += l.x;
+        run.y += l.y;
+        cum[i] = run;
+      }
+      reinterpret_cast<float2*>(group_sum + tg * 64)[kp] = run;
+      // V operand: rows = token, 64 contiguous value columns (MN-major); bf16 is copied, fp16 is split
+      {
+        const uint8_t* raw_v = smem + kOffRaw + 3 * kRawTile;
+        const int s = tid >> 3, vc = tid & 7;  // 256 chunks of 8 values
+        uint4 q = *reinterpret_cast<const uint4*>(raw_v + s * 128 + vc * 16);
+        uint8_t* dst = smem + kOffV + vc * kStride32 + (s & 7) * 16 + (s >> 3) * kRowGroup;
+        if (s >= rows) q = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (kVExact) {
+          *reinterpret_cast<uint4*>(dst) = q;
+        } else {
+          float x[8];
+          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2<io_t>(words[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+          }
+          uint4 hi, lo;
+          split8(x, hi, lo);
+          *reinterpret_cast<uint4*>(dst) = hi;
+          *reinterpret_cast<uint4*>(dst + kTileV) = lo;
+        }
+      }
+      __syncthreads();
+      float2 off = make_float2(0.f, 0.f);
+      for (int g = 0; g < tg; ++g) {
+        const float2 sgrp = reinterpret_cast<const float2*>(group_sum + g * 64)[kp];
+        off.x += sgrp.x;
+        off.y += sgrp.y;
+      }
+      float2 g_prev = make_float2(fast_exp2(off.x), fast_exp2(off.y));
+      uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kStride64 + (kp & 3) * 4;
+      uint8_t* x2 = smem + kOffX2 + (kp >> 2) * kStride64 + (kp & 3) * 4;
+#pragma unroll
+      for (int i = 0; i < kRowsPerWarp; ++i) {
+        const int t = tg * kRowsPerWarp + i;
+        const bool live = t < rows;
+        const float2 lg = make_float2(off.x + cum[i].x, off.y + cum[i].y);
+        const float2 g = make_float2(fast_exp2(lg.x), fast_exp2(lg.y));
+        const float2 gi = make_float2(fast_exp2(-lg.x), fast_exp2(-lg.y));
+        const float2 gx = g_prev;  // exclusive product = inclusive product of the previous row
+        g_prev = g;
+        float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
+        float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
+        float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
+        float2 b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
+        if (!live) {
+          r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
+        }
+        const uint32_t row_lo = (t >> 3) * kRowGroup + (t & 7) * 16;         // rows 0..31
+        const uint32_t row_hi = ((t + 32) >> 3) * kRowGroup + (t & 7) * 16;  // rows 32..63
+        uint32_t h, l;
+        split2(a2.x * gx.x, a2.y * gx.y, h, l);
+        *reinterpret_cast<uint32_t*>(x1 + row_lo) = h;
+        *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_lo) = l;
+        split2(r2.x * g.x, r2.y * g.y, h, l);
+        *reinterpret_cast<uint32_t*>(x1 + row_hi) = h;
+        *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_hi) = l;
+        split2(b2.x * gi.x, b2.y * gi.y, h, l);
+        *reinterpret_cast<uint32_t*>(x2 + row_lo) = h;
+        *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_lo) = l;
+        split2(k2.x * gi.x, k2.y * gi.y, h, l);
+        *reinterpret_cast<uint32_t*>(x2 + row_hi) = h;
+        *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_hi) = l;
+        if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_l)[kp] = g;
+      }
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= P = X1 X2^T ; Q = X1 S0 =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
+      issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
+      mma_commit(bar_mma);
+    }
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+
+    // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
+    {
+      // accumulator row arow: rows 0..31 belong to At (quadrants 0,1), rows 32..63 to Rt (quadrants 2,3);
+      // columns 32*half..: half 0 = products with Bt (A_ab / A_rb), half 1 = with Kt (A_ak / A_rk)
+      uint32_t regs[32];
+      tmem_ld32(tmem_lane + kColP + half * 32, regs);
+      tmem_ld_wait();
+      if (row_lane) {
+        const int t = arow & 31;
+        const int limit = quad < 2 ? t : t + 1;  // keep columns s < limit
+        float vals[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vals[i] = i < limit ? __uint_as_float(regs[i]) : 0.0f;
+        if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
+          float4* dst = reinterpret_cast<float4*>(smem + kOffAb + t * kInvLd * 4);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dst[j] = make_float4(vals[4 * j], vals[4 * j + 1], vals[4 * j + 2], vals[4 * j + 3]);
+        } else {
+          // half 1: A_ak -> X3 row t (quad<2), A_rk -> X3 row 32+t (quad>=2); half 0, quad>=2: A_rb -> X4 row 32+t
+          uint8_t* dst = smem + (half == 1 ? kOffX3 : kOffX4) + (arow >> 3) * kRowGroup + (arow & 7) * 16;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 hi, lo;
+            split8(vals + 8 * j, hi, lo);
+            *reinterpret_cast<uint4*>(dst + j * kStride64) = hi;
+            *reinterpret_cast<uint4*>(dst + kTileK32 + j * kStride64) = lo;
+          }
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
+      mma_commit(bar_mma);
+    }
+    {
+      float* ab = reinterpret_cast<float*>(smem + kOffAb);
+      float* ti = reinterpret_cast<float*>(smem + kOffTi);
+      float* mb = reinterpret_cast<float*>(smem + kOffMb);
+      // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread
+      if (tid < 32) {
+        const int d = tid >> 4, j = tid & 15;
+        const float* blk = ab + (16 * d) * kInvLd + 16 * d;
+        float x[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          float row[16];
+#pragma unroll
+          for (int q4 = 0; q4 < (t + 3) / 4; ++q4) {
+            const float4 f = *reinterpret_cast<const float4*>(blk + t * kInvLd + 4 * q4);
+            row[4 * q4] = f.x; row[4 * q4 + 1] = f.y; row[4 * q4 + 2] = f.z; row[4 * q4 + 3] = f.w;
+          }
+          float acc0 = t == j ? 1.0f : 0.0f, acc1 = 0.0f;
+#pragma unroll
+          for (int s2 = 0; s2 < t; ++s2) {
+            if (s2 & 1) acc1 = fmaf(row[s2], x[s2], acc1);
+            else acc0 = fmaf(row[s2], x[s2], acc0);
+          }
+          x[t] = acc0 + acc1;
+          ti[(16 * d + t) * kInvLd + 16 * d + j] = x[t];
+        }
+      } else {  // zero the block above the diagonal: rows 0..15, columns 16..31
+        const int e = tid - 32;
+        if (e < 224) {
+          ti[(e >> 4) * kInvLd + 16 + (e & 15)] = 0.0f;
+          if (e < 32) ti[(14 + (e >> 4)) * kInvLd + 16 + (e & 15)] = 0.0f;
+        }
+      }
+      __syncthreads();
+      // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
+      {
+        const int rr = tid >> 4, cc = tid & 15;
+        float acc = 0.0f;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const float4 av = *reinterpret_cast<const float4*>(ab + (16 + rr) * kInvLd + 4 * s4);
+          acc = fmaf(av.x, ti[(4 * s4 + 0) * kInvLd + cc], acc);
+          acc = fmaf(av.y, ti[(4 * s4 + 1) * kInvLd + cc], acc);
+          acc = fmaf(av.z, ti[(4 * s4 + 2) * kInvLd + cc], acc);
+          acc = fmaf(av.w, ti[(4 * s4 + 3) * kInvLd + cc], acc);
+        }
+        mb[rr * kMbLd + cc] = acc;
+        __syncthreads();
+        acc = 0.0f;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const float4 dv = *reinterpret_cast<const float4*>(ti + (16 + rr) * kInvLd + 16 + 4 * s4);
+          acc = fmaf(dv.x, mb[(4 * s4 + 0) * kMbLd + cc], acc);
+          acc = fmaf(dv.y, mb[(4 * s4 + 1) * kMbLd + cc], acc);
+          acc = fmaf(dv.z, mb[(4 * s4 + 2) * kMbLd + cc], acc);
+          acc = fmaf(dv.w, mb[(4 * s4 + 3) * kMbLd + cc], acc);
+        }
+        ti[(16 + rr) * kInvLd + cc] = acc;
+      }
+      __syncthreads();
+      // T -> rows 0..31 of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
+      if (tid < 128) {
+        const int t = tid >> 2, cj = tid & 3;
+        const float4 f0 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8);
+        const float4 f1 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8 + 4);
+        const float x[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+        uint4 hi, lo;
+        split8(x, hi, lo);
+        uint8_t* dst = smem + kOffX4 + (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64;
+        *reinterpret_cast<uint4*>(dst) = hi;
+        *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
+      }
+    }
+    // wait for Q, then W = Q rows 0..31 -> operand tile (rows = token, MN-major)
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+    auto rows_to_operand = [&](uint32_t col) {  // accumulator rows 0..31 x 64 columns at `col` -> kOffOp
+      if (quad < 2) {
+        uint32_t regs[32];
+        tmem_ld32(tmem_lane + col + half * 32, regs);
+        tmem_ld_wait();
+        if (row_lane) store_operand_row(arow, regs);
+      }
+    };
+    rows_to_operand(kColQ);
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= U = T W  (rows 32..63 of this product are unused) =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      if (c + 1 < n_chunks) issue_tma(c + 1);  // the staging area (and the inverse scratch in it) is free
+      issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
+      mma_commit(bar_mma);
+    }
+    if (c + 1 < n_chunks) tma_in_flight = true;
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+    rows_to_operand(kColU);
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+
+    // ================= Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V =================
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
+      issue_gemm<true, true, 2>(tmem + kColS, op_bt, op_rows, idesc_mnmn, true);
+      issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
+      mma_commit(bar_mma);
+    }
+    {
+      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
+      ++mma_uses;
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
+    }
+    // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
+    if (quad >= 2) {
+      uint32_t regs[32];
+      tmem_ld32(tmem_lane + kColQ + half * 32, regs);
+      tmem_ld_wait();
+      const int t = arow - 32;
+      if (row_lane && t < rows) {
+        const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32;
+        io_t* yp = static_cast<io_t*>(p.y) + out;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          alignas(16) io_t packed[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) packed[e] = from_f32<io_t>(__uint_as_float(regs[8 * j + e]) * p.scale);
+          *reinterpret_cast<uint4*>(yp + 8 * j) = *reinterpret_cast<const uint4*>(packed);
+        }
+        if (p.y_f32 != nullptr) {
+          float4* yf = reinterpret_cast<float4*>(p.y_f32 + out);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            yf[j] = make_float4(__uint_as_float(regs[4 * j]) * p.scale, __uint_as_float(regs[4 * j + 1]) * p.scale,
+                                __uint_as_float(regs[4 * j + 2]) * p.scale, __uint_as_float(regs[4 * j + 3]) * p.scale);
+        }
+      }
+    }
+    // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
+    {
+      uint32_t regs[32];
+      tmem_ld32(tmem_lane + kColS + half * 32, regs);
+      tmem_ld_wait();
+      const float gl = gamma_l[arow];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) regs[i] = __float_as_uint(__uint_as_float(regs[i]) * gl);
+      if (c + 1 < n_chunks) {
+        tmem_st32(tmem_lane + kColS + half * 32, regs);
+        if (row_lane) store_operand_row(arow, regs);
+        tmem_st_wait();
+      } else if (row_lane) {
+        float4* dst = reinterpret_cast<float4*>(state_g + arow * kHeadDim + half * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          __stcs(dst + i, make_float4(__uint_as_float(regs[4 * i]), __uint_as_float(regs[4 * i + 1]),
+                                      __uint_as_float(regs[4 * i + 2]), __uint_as_float(regs[4 * i + 3])));
+      }
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+  }
+
+  if (failed) {
+    if (tid == 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 1);
+    if (tma_in_flight) mbar_wait(bar_tma, tma_parity, 200000u);  // bounded drain of the load in flight
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <typename io_t>
+int launch_typed32(const ChunkParams& p, const Maps& maps, bool logits, cudaStream_t stream) {
+  auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true> : wkv7_chunk32_tc_kernel<io_t, false>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return check_launch("wkv7_chunk32_tc_kernel shared-memory attribute");
+  const long long ctas = static_cast<long long>(p.n_seq) * p.heads;
+  if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: too many (sequence, head) pairs");
+  kernel<<<static_cast<unsigned>(ctas), kThreads, kSmemBytes, stream>>>(p, maps);
+  return check_launch("wkv7_chunk32_tc_kernel");
+}
+
+}  // namespace
+
+int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
+                      const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
+                      void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
+                      float scale, int32_t* error_flag, cudaStream_t stream) {
+  const bool bf16 = io_dtype == FRWKV_IO_BF16;
+  chunk::Maps maps;
+  const int map_rc = chunk::make_maps(&maps, r, w, k, v, a, b, total_tokens, heads, bf16, kChunk);
+  if (map_rc != FRWKV_OK) return map_rc;
+  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale};
+  const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
+  if (bf16) return launch_typed32<__nv_bfloat16>(p, maps, logits, stream);
+  return launch_typed32<__half>(p, maps, logits, stream);
+}
+
+}  // namespace frwkv

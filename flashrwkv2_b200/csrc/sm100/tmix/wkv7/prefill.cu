@@ -15,12 +15,33 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
                             int max_seqlen, int parts_override, cudaStream_t stream);
-int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool,
-                    const void* r, const void* w, const void* k, const void* v, const void* a,
-                    const void* b, const void* bias, void* y, float* y_f32, int n_seq, int total_tokens,
-                    int heads, int io_dtype, int decay_mode, float scale, int max_seqlen, void* workspace,
-                    size_t workspace_bytes, int32_t* error_flag, cudaStream_t stream);
-size_t chunk_tc_workspace_bytes(int n_seq, int total_tokens, int heads);
+int launch_chunk64_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
+                      const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
+                      void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
+                      float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                      cudaStream_t stream);
+int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
+                      const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
+                      void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
+                      float scale, int32_t* error_flag, cudaStream_t stream);
+
+size_t chunk_tc_workspace_bytes(int, int, int) { return 0; }
+
+// Chunk length of the tensor-core kernel: 32-row chunks keep two CTAs resident per SM, 64-row chunks
+// do more work per barrier.  FRWKV_PREFILL_CHUNK=32|64 overrides the default (tuning / test hook).
+int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
+                    const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
+                    void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
+                    float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                    cudaStream_t stream) {
+  int chunk = 64;
+  if (const char* e = std::getenv("FRWKV_PREFILL_CHUNK")) chunk = std::atoi(e);
+  if (chunk == 32)
+    return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
+                             io_dtype, decay_mode, scale, error_flag, stream);
+  return launch_chunk64_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
+                           io_dtype, decay_mode, scale, max_seqlen, workspace, workspace_bytes, error_flag, stream);
+}
 
 }  // namespace frwkv
 
