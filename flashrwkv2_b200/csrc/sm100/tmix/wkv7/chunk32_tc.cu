@@ -43,13 +43,14 @@ constexpr uint32_t kOffMisc = kOffV + 2 * kTileV;     // gamma_L[64], group sums
 constexpr uint32_t kMiscBytes = 64 * 4 + kWarps * 64 * 4 + 64;
 constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 128;
 static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM's shared memory");
-// fp32 scratch of the 32x32 inverse, aliased onto the TMA staging area (free after stage A)
+// fp32 scratch of the 32x32 inverse, aliased onto [At; Rt] (dead once P and Q are complete), so that
+// the TMA staging area is free as soon as stage A is done and the next chunk's load can start then
 constexpr int kInvLd = 36;
-constexpr uint32_t kOffAb = kOffRaw;                   // A_ab [32][36]
+constexpr uint32_t kOffAb = kOffX1;                    // A_ab [32][36]
 constexpr uint32_t kOffTi = kOffAb + 32 * kInvLd * 4;  // T    [32][36]
 constexpr int kMbLd = 17;
 constexpr uint32_t kOffMb = kOffTi + 32 * kInvLd * 4;  // block product [16][17]
-static_assert(kOffMb + 16 * kMbLd * 4 <= kOffX1, "inverse scratch must fit in the staging area");
+static_assert(kOffMb + 16 * kMbLd * 4 <= kOffX2, "inverse scratch must fit in the [At; Rt] tile");
 
 // ---- TMEM map (columns) --------------------------------------------------------------------
 constexpr uint32_t kTmemCols = 256;
@@ -107,7 +108,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
-  auto issue_tma = [&](int chunk_index) {  // thread 0 only
+  auto issue_tma = [&](int chunk_index) {  // one thread
     const int row = t_begin + chunk_index * kChunk;
     mbar_expect_tx(bar_tma, 6 * kRawTile);
     tma_load_3d(smem + kOffRaw + 0 * kRawTile, &maps.r, bar_tma, 0, head, row);
@@ -177,6 +178,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
   uint32_t mma_uses = 0;
   bool failed = false;
+#ifdef FRWKV_CHUNK_TIMING
+  long long phase_t0 = clock64();
+#endif
   const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
 
   for (int c = 0; c < n_chunks; ++c) {
@@ -190,6 +194,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       tma_in_flight = false;
       tma_parity ^= 1u;
     }
+    FRWKV_PHASE(0)
     {
       constexpr int kRowsPerWarp = kChunk / kWarps;  // 4
       const int kp = lane;                           // key channels 2*kp, 2*kp+1
@@ -246,11 +251,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         }
       }
       __syncthreads();
+      FRWKV_PHASE(12)
       float2 off = make_float2(0.f, 0.f);
-      for (int g = 0; g < tg; ++g) {
+#pragma unroll
+      for (int g = 0; g < kWarps - 1; ++g) {  // loads issued together; only the adds are a chain
         const float2 sgrp = reinterpret_cast<const float2*>(group_sum + g * 64)[kp];
-        off.x += sgrp.x;
-        off.y += sgrp.y;
+        if (g < tg) {
+          off.x += sgrp.x;
+          off.y += sgrp.y;
+        }
       }
       float2 g_prev = make_float2(fast_exp2(off.x), fast_exp2(off.y));
       uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kStride64 + (kp & 3) * 4;
@@ -293,6 +302,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(1)
+    // the staging area has been consumed: start the next chunk's load (a thread other than the MMA issuer)
+    if (tid == 32 && c + 1 < n_chunks) issue_tma(c + 1);
+    if (c + 1 < n_chunks) tma_in_flight = true;
     // ================= P = X1 X2^T ; Q = X1 S0 =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
@@ -307,6 +320,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       tcgen05_fence_after_sync();
     }
 
+    FRWKV_PHASE(2)
     // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
     {
       // accumulator row arow: rows 0..31 belong to At (quadrants 0,1), rows 32..63 to Rt (quadrants 2,3);
@@ -341,6 +355,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(3)
     // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
@@ -355,23 +370,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (tid < 32) {
         const int d = tid >> 4, j = tid & 15;
         const float* blk = ab + (16 * d) * kInvLd + 16 * d;
-        float x[16];
+        float part[16];  // right-looking substitution: part[t] collects the row sums as columns finish
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          float row[16];
+        for (int t = 0; t < 16; ++t) part[t] = t == j ? 1.0f : 0.0f;
 #pragma unroll
-          for (int q4 = 0; q4 < (t + 3) / 4; ++q4) {
-            const float4 f = *reinterpret_cast<const float4*>(blk + t * kInvLd + 4 * q4);
-            row[4 * q4] = f.x; row[4 * q4 + 1] = f.y; row[4 * q4 + 2] = f.z; row[4 * q4 + 3] = f.w;
-          }
-          float acc0 = t == j ? 1.0f : 0.0f, acc1 = 0.0f;
+        for (int s2 = 0; s2 < 16; ++s2) {
+          const float xs = part[s2];  // x[s2] is final: every earlier column has been folded in
+          ti[(16 * d + s2) * kInvLd + 16 * d + j] = xs;
 #pragma unroll
-          for (int s2 = 0; s2 < t; ++s2) {
-            if (s2 & 1) acc1 = fmaf(row[s2], x[s2], acc1);
-            else acc0 = fmaf(row[s2], x[s2], acc0);
-          }
-          x[t] = acc0 + acc1;
-          ti[(16 * d + t) * kInvLd + 16 * d + j] = x[t];
+          for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
         }
       } else {  // zero the block above the diagonal: rows 0..15, columns 16..31
         const int e = tid - 32;
@@ -381,6 +388,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         }
       }
       __syncthreads();
+      FRWKV_PHASE(10)
       // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
       {
         const int rr = tid >> 4, cc = tid & 15;
@@ -407,6 +415,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         ti[(16 + rr) * kInvLd + cc] = acc;
       }
       __syncthreads();
+      FRWKV_PHASE(11)
       // T -> rows 0..31 of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
       if (tid < 128) {
         const int t = tid >> 2, cj = tid & 3;
@@ -420,6 +429,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
       }
     }
+    FRWKV_PHASE(4)
     // wait for Q, then W = Q rows 0..31 -> operand tile (rows = token, MN-major)
     {
       const bool ok = mbar_wait(bar_mma, mma_uses & 1);
@@ -440,25 +450,26 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(5)
     // ================= U = T W  (rows 32..63 of this product are unused) =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
-      if (c + 1 < n_chunks) issue_tma(c + 1);  // the staging area (and the inverse scratch in it) is free
       issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
       mma_commit(bar_mma);
     }
-    if (c + 1 < n_chunks) tma_in_flight = true;
     {
       const bool ok = mbar_wait(bar_mma, mma_uses & 1);
       ++mma_uses;
       if (__syncthreads_or(!ok)) { failed = true; break; }
       tcgen05_fence_after_sync();
     }
+    FRWKV_PHASE(6)
     rows_to_operand(kColU);
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
     __syncthreads();
 
+    FRWKV_PHASE(7)
     // ================= Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
@@ -473,6 +484,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (__syncthreads_or(!ok)) { failed = true; break; }
       tcgen05_fence_after_sync();
     }
+    FRWKV_PHASE(8)
     // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
     if (quad >= 2) {
       uint32_t regs[32];
@@ -522,6 +534,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     __syncthreads();
     tcgen05_fence_after_sync();
+    FRWKV_PHASE(9)
   }
 
   if (failed) {

@@ -379,23 +379,15 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (tid < 64) {
         const int d = tid >> 4, j = tid & 15;
         const float* blk = ab + (16 * d) * kInvLd + 16 * d;
-        float x[16];
+        float part[16];  // right-looking substitution: part[t] collects the row sums as columns finish
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          float row[16];
+        for (int t = 0; t < 16; ++t) part[t] = t == j ? 1.0f : 0.0f;
 #pragma unroll
-          for (int q4 = 0; q4 < (t + 3) / 4; ++q4) {
-            const float4 f = *reinterpret_cast<const float4*>(blk + t * kInvLd + 4 * q4);
-            row[4 * q4] = f.x; row[4 * q4 + 1] = f.y; row[4 * q4 + 2] = f.z; row[4 * q4 + 3] = f.w;
-          }
-          float acc0 = t == j ? 1.0f : 0.0f, acc1 = 0.0f;
+        for (int s2 = 0; s2 < 16; ++s2) {
+          const float xs = part[s2];  // x[s2] is final: every earlier column has been folded in
+          ti[(16 * d + s2) * kInvLd + 16 * d + j] = xs;
 #pragma unroll
-          for (int s2 = 0; s2 < t; ++s2) {
-            if (s2 & 1) acc1 = fmaf(row[s2], x[s2], acc1);
-            else acc0 = fmaf(row[s2], x[s2], acc0);
-          }
-          x[t] = acc0 + acc1;
-          ti[(16 * d + t) * kInvLd + 16 * d + j] = x[t];
+          for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
         }
       } else {  // zero everything above the block diagonal: 16-blocks (0,1), (2,3) and the 32-block (0,1)
         for (int e = tid - 64; e < 512 + 1024; e += kThreads - 64) {

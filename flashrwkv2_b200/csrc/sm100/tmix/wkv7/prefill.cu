@@ -34,7 +34,7 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
                     float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
                     cudaStream_t stream) {
-  int chunk = 64;
+  int chunk = 32;
   if (const char* e = std::getenv("FRWKV_PREFILL_CHUNK")) chunk = std::atoi(e);
   if (chunk == 32)
     return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
