@@ -31,6 +31,57 @@ def sources() -> list[Path]:
     return sorted(CSRC.rglob("*.cu"))
 
 
+BINDINGS = PKG / "csrc" / "bindings"
+EXT = PKG / "_C_sm100.so"
+
+
+def build_extension(force: bool = False) -> Path:
+    """Compile the pybind/torch shim (_C_sm100) with g++ and link it against libfrwkv_sm100.so."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension
+
+    srcs = sorted(BINDINGS.glob("*.cpp"))
+    h = hashlib.sha256(torch.__version__.encode())
+    for f in srcs + sorted(BINDINGS.glob("*.h")) + sorted((PKG.parent / "include").glob("*.h")):
+        h.update(f.read_bytes())
+    stamp = LIB_DIR / ".ext_digest"
+    digest = h.hexdigest()
+    if EXT.exists() and stamp.exists() and stamp.read_text() == digest and not force:
+        return EXT
+    inc = [f"-I{d}" for d in cpp_extension.include_paths(device_type="cuda")]
+    inc += [f"-I{sysconfig.get_paths()['include']}", f"-I{PKG.parent / 'include'}"]
+    flags = ["-O2", "-fPIC", "-std=c++17", "-DTORCH_EXTENSION_NAME=_C_sm100", "-DTORCH_API_INCLUDE_EXTENSION_H",
+             "-DFLASHRWKV_BACKEND_SM100=1", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+             "-Wno-deprecated-declarations"]
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    ext_obj = PKG / "build" / "ext"
+    ext_obj.mkdir(parents=True, exist_ok=True)
+
+    def compile_one(src: Path) -> Path:
+        obj = ext_obj / (src.stem + ".o")
+        res = subprocess.run(["g++", *flags, *inc, "-c", str(src), "-o", str(obj)], capture_output=True, text=True,
+                             env=env)
+        if res.returncode != 0:
+            raise RuntimeError(f"g++ failed for {src}:\n{res.stderr[-4000:]}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=len(srcs)) as pool:
+        objs = list(pool.map(compile_one, srcs))
+    libdirs = cpp_extension.library_paths(device_type="cuda")
+    cmd = ["g++", "-shared", "-o", str(EXT), *map(str, objs), *[f"-L{d}" for d in libdirs], f"-L{LIB_DIR}",
+           "-lfrwkv_sm100", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+           "-lcudart", "-Wl,-rpath,$ORIGIN/lib"]
+    res = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if res.returncode != 0:
+        raise RuntimeError(f"link of _C_sm100 failed:\n{res.stderr[-4000:]}")
+    stamp.write_text(digest)
+    return EXT
+
+
 def _nvcc() -> str:
     found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(found).exists():
@@ -95,3 +146,4 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    print(build_extension(force="--force" in sys.argv))

@@ -56,9 +56,10 @@ def test_operators_fail_loudly_without_backend(monkeypatch):
 
 def test_library_loads_and_exports_every_declared_symbol():
     from flashrwkv2_b200 import _lib
-    from flashrwkv2_b200.build import build
+    from flashrwkv2_b200.build import build, build_extension
 
     build()
+    build_extension()
     header = (ROOT / "include" / "frwkv_sm100.h").read_text()
     declared = set(re.findall(r"\b(frwkv_sm100_\w+)\s*\(", header))
     assert declared == set(_lib.SYMBOLS)
@@ -82,13 +83,23 @@ def test_native_module_exports_reference_symbols():
                  "tmix_wkv7_recurrent_fp32_from_decay_logits", "rl_infctx_tmix_wkv7_chunk_fp32io16_forward",
                  "_RecurrentMetadataTicket", "tmix_wkv7_prefill_fp32"):
         assert hasattr(ext, name), name
-    sig = inspect.signature(ext.tmix_wkv7_recurrent_fp32_from_decay_logits)
-    assert list(sig.parameters)[:14] == ["query_start_loc", "state_indices", "state", "r", "decay_logits", "k", "v",
-                                         "a", "b", "output", "scale", "decay_bias", "validated_metadata",
-                                         "max_seqlen"]
-    sig = inspect.signature(ext.rl_infctx_tmix_wkv7_chunk_fp32io16_forward)
-    assert list(sig.parameters)[:13] == ["sequence_chunk_offsets", "chunk_token_starts", "chunk_token_ends", "state",
-                                         "r", "decay_logits", "k", "v", "a", "b", "strategy", "scale", "decay_bias"]
+    def arg_names(fn):  # pybind functions carry their signature in the first docstring line
+        head = fn.__doc__.splitlines()[0]
+        return [piece.split(":")[0].strip() for piece in head[head.index("(") + 1:head.rindex(")")].split(", ")
+                if ":" in piece]
+
+    assert arg_names(ext.tmix_wkv7_recurrent_fp32_from_decay_logits)[:14] == [
+        "query_start_loc", "state_indices", "state", "r", "decay_logits", "k", "v", "a", "b", "output", "scale",
+        "decay_bias", "validated_metadata", "max_seqlen"]
+    assert arg_names(ext.rl_infctx_tmix_wkv7_chunk_fp32io16_forward)[:13] == [
+        "sequence_chunk_offsets", "chunk_token_starts", "chunk_token_ends", "state", "r", "decay_logits", "k", "v",
+        "a", "b", "strategy", "scale", "decay_bias"]
+    assert arg_names(ext.prepare_tmix_wkv7_recurrent_metadata) == [
+        "query_start_loc", "state_indices", "total_tokens", "state_pool_size", "max_seqlen"]
+    assert arg_names(ext.prepare_tmix_wkv7_recurrent_graph_metadata) == [
+        "query_start_loc", "state_indices", "num_active_tokens", "num_active_sequences", "token_capacity",
+        "sequence_capacity", "state_pool_size", "max_seqlen_capacity"]
+    assert ext.__file__.endswith(".so"), "the native module must be the compiled extension"
     for method in ("_check_compatible", "_query_start_loc_snapshot", "_state_indices_snapshot", "_status",
                    "_max_seqlen", "_is_graph", "_num_active_tokens", "_num_active_sequences"):
         assert hasattr(ext._RecurrentMetadataTicket, method)
