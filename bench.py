@@ -113,13 +113,15 @@ class ClockSampler:
                 "samples": len(sm), "power_w_max": max(power)}
 
 
-def _event_time_ms(fn, steps, stream=None):
+def _event_time_ms(fn, steps, finish=None):
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     start.record()
     for i in range(steps):
         fn(i)
+    if finish is not None:
+        finish()
     end.record()
     end.synchronize()
     return start.elapsed_time(end)
@@ -229,29 +231,41 @@ def run_ours(args, rank, local_rank, world):
     if args.no_e2e or h2d > 8 * 2**30:  # bound pinned host memory on shared boxes
         clocks = sampler.stop()
     else:
-        host = {n: src[n].cpu().pin_memory() for n in "rwkvab"}
-        dev_in = {n: torch.empty_like(src[n]) for n in "rwkvab"}
-        y_host = torch.empty(src["v"].shape, dtype=src["v"].dtype).pin_memory()
+        # the caller's six token tensors live in one pinned host block -> one host->device copy per step;
+        # y goes back on a second stream so that it overlaps the next step's upload (PCIe is full duplex)
+        host = torch.stack([src[n].cpu() for n in "rwkvab"]).pin_memory()
+        dev_in = torch.empty_like(host, device=device)
+        y_host = [torch.empty(src["v"].shape, dtype=src["v"].dtype).pin_memory() for _ in range(2)]
         pool = src["state_pool"]
         cu, slots = src["cu_seqlens"], src["state_indices"]
         ticket = ops.prepare_tmix_wkv7_recurrent_metadata(cu, slots, total_tokens=tokens_per_step,
                                                           state_pool_size=pool.shape[0])
         op = (ops.infer_tmix_wkv7_recurrent_fp32io16_forward_varlen if is_decode
               else ops.infer_tmix_wkv7_prefill_fp32io16_forward_varlen)
+        main_stream = torch.cuda.current_stream()
+        copy_stream = torch.cuda.Stream()
+        uploaded = [torch.cuda.Event(), torch.cuda.Event()]
 
         def e2e_step(i):
-            for n in "rwkvab":
-                dev_in[n].copy_(host[n], non_blocking=True)
-            out = op(dev_in["r"], dev_in["w"], dev_in["k"], dev_in["v"], dev_in["a"], dev_in["b"], state_pool=pool,
+            dev_in.copy_(host, non_blocking=True)
+            out = op(dev_in[0], dev_in[1], dev_in[2], dev_in[3], dev_in[4], dev_in[5], state_pool=pool,
                      cu_seqlens=cu, state_indices=slots, validated_metadata=ticket, decay_mode="retention")
-            y_host.copy_(out, non_blocking=True)
+            done = uploaded[i % 2]
+            done.record(main_stream)
+            copy_stream.wait_event(done)
+            with torch.cuda.stream(copy_stream):
+                y_host[i % 2].copy_(out, non_blocking=True)
+            out.record_stream(copy_stream)
+
+        def e2e_finish():
+            main_stream.wait_stream(copy_stream)
 
         e2e_steps = max(3, min(args.steps, 2000 if is_decode else 20))
         for i in range(min(args.warmup, 10)):
             e2e_step(i)
         torch.cuda.synchronize()
         fdist.barrier()
-        e2e_ms = _event_time_ms(e2e_step, e2e_steps)
+        e2e_ms = _event_time_ms(e2e_step, e2e_steps, e2e_finish)
         fdist.barrier()
         e2e_ms = fdist.reduce_max(e2e_ms)
         clocks = sampler.stop()
@@ -379,6 +393,8 @@ def run_reference(args, rank, world):
 
     if rank != 0:
         return None
+    # torchrun pins OMP_NUM_THREADS=1; the CPU path gets every host thread it can use
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     name = args.workload
     per_rank_n = 2048 if name == "c4_decode" else None
     wl = make_workload(name, n_seq=per_rank_n) if name in ("c1", "c4_decode") else make_workload(
