@@ -84,12 +84,14 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   float* group_sum = gamma_l + 64;  // [8][64] log2-decay sums of each 4-row group
   uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_sum + kWarps * 64);
   uint64_t* bar_mma = bar_tma + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
+  uint64_t* bar_state = bar_tma + 2;  // its own barrier: two commits may not complete two phases of one
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_state + 1);
   const uint32_t sbase = smem_u32(smem);
 
   if (tid == 0) {
     mbar_init(bar_tma, 1);
     mbar_init(bar_mma, 1);
+    mbar_init(bar_state, 1);
     mbar_fence_init();
     tma_prefetch_descriptor(&maps.r);
     tma_prefetch_descriptor(&maps.w);
@@ -366,9 +368,12 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       float* ab = reinterpret_cast<float*>(smem + kOffAb);
       float* ti = reinterpret_cast<float*>(smem + kOffTi);
       float* mb = reinterpret_cast<float*>(smem + kOffMb);
-      // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread
-      if (tid < 32) {
-        const int d = tid >> 4, j = tid & 15;
+      bool w_ready = true;
+      // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread, on a warp
+      // that has no accumulator rows to read back; meanwhile the warps of quadrants 0,1 wait for Q and
+      // turn W = Q rows 0..31 into the operand tile, and the remaining warps clear T's upper block
+      if (warp == 2) {
+        const int d = lane >> 4, j = lane & 15;
         const float* blk = ab + (16 * d) * kInvLd + 16 * d;
         float part[16];  // right-looking substitution: part[t] collects the row sums as columns finish
 #pragma unroll
@@ -380,14 +385,21 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
           for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
         }
-      } else {  // zero the block above the diagonal: rows 0..15, columns 16..31
-        const int e = tid - 32;
-        if (e < 224) {
-          ti[(e >> 4) * kInvLd + 16 + (e & 15)] = 0.0f;
-          if (e < 32) ti[(14 + (e >> 4)) * kInvLd + 16 + (e & 15)] = 0.0f;
+      } else if (quad >= 2) {  // warps 3, 6, 7: zero the block above the diagonal (rows 0..15, columns 16..31)
+        const int e0 = (warp == 3 ? 0 : warp == 6 ? 1 : 2) * 32 + lane;
+        for (int e = e0; e < 256; e += 96) ti[(e >> 4) * kInvLd + 16 + (e & 15)] = 0.0f;
+      } else {
+        w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_uses & 1));
+        tcgen05_fence_after_sync();
+        if (w_ready) {
+          uint32_t regs[32];
+          tmem_ld32(tmem_lane + kColQ + half * 32, regs);
+          tmem_ld_wait();
+          if (row_lane) store_operand_row(arow, regs);
         }
       }
-      __syncthreads();
+      ++mma_uses;
+      if (__syncthreads_or(!w_ready)) { failed = true; break; }
       FRWKV_PHASE(10)
       // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
       {
@@ -430,13 +442,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
     }
     FRWKV_PHASE(4)
-    // wait for Q, then W = Q rows 0..31 -> operand tile (rows = token, MN-major)
-    {
-      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
-      ++mma_uses;
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tcgen05_fence_after_sync();
-    }
     auto rows_to_operand = [&](uint32_t col) {  // accumulator rows 0..31 x 64 columns at `col` -> kOffOp
       if (quad < 2) {
         uint32_t regs[32];
@@ -445,7 +450,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         if (row_lane) store_operand_row(arow, regs);
       }
     };
-    rows_to_operand(kColQ);
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
     __syncthreads();
@@ -474,9 +478,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     if (tid == 0) {
       tcgen05_fence_after_sync();
       issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
+      mma_commit(bar_mma);  // Y is complete when this one arrives ...
       issue_gemm<true, true, 2>(tmem + kColS, op_bt, op_rows, idesc_mnmn, true);
       issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
-      mma_commit(bar_mma);
+      mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMAs
     }
     {
       const bool ok = mbar_wait(bar_mma, mma_uses & 1);
@@ -509,6 +514,11 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
                                 __uint_as_float(regs[4 * j + 2]) * p.scale, __uint_as_float(regs[4 * j + 3]) * p.scale);
         }
       }
+    }
+    {
+      const bool ok = mbar_wait(bar_state, c & 1);
+      if (__syncthreads_or(!ok)) { failed = true; break; }
+      tcgen05_fence_after_sync();
     }
     // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
     {
