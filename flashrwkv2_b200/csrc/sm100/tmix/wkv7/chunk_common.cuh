@@ -39,6 +39,7 @@ struct ChunkParams {
   int* error_flag;
   int n_seq, total_tokens, heads;
   float scale;
+  const int* order;  // CTA rank -> sequence, longest first (nullptr: natural order)
 };
 
 struct Maps {

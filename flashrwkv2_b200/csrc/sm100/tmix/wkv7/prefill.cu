@@ -18,14 +18,45 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
 int launch_chunk64_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
-                      cudaStream_t stream);
+                      float scale, const int32_t* order, int32_t* error_flag, cudaStream_t stream);
 int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, int32_t* error_flag, cudaStream_t stream);
+                      float scale, const int32_t* order, int32_t* error_flag, cudaStream_t stream);
 
-size_t chunk_tc_workspace_bytes(int, int, int) { return 0; }
+namespace {
+
+// Ragged batches: CTAs are handed to SMs in grid order, and a CTA's run time is proportional to its
+// sequence length, so the tail of the launch is as long as whichever long sequence happens to start
+// last.  With the sequences ranked longest-first the tail shrinks to the shortest ones.  The ranking is
+// one small kernel (rank of i = number of sequences that are longer, ties by index) writing
+// order[rank] = i into caller-provided scratch; batches above kMaxOrdered sequences keep their natural
+// order (their tail is negligible and an all-pairs ranking would not be).
+constexpr int kMaxOrdered = 2048;
+constexpr int kOrderThreads = 1024;
+
+__global__ void __launch_bounds__(kOrderThreads) sequence_order_kernel(const int* __restrict__ cu,
+                                                                       const int* __restrict__ status, int n_seq,
+                                                                       int* __restrict__ order) {
+  __shared__ int len[kMaxOrdered];
+  const bool valid = status == nullptr || status[0] == 0;
+  const int active = status == nullptr ? n_seq : status[2];
+  for (int i = threadIdx.x; i < n_seq; i += kOrderThreads)
+    len[i] = (valid && i < active) ? max(cu[i + 1] - cu[i], 0) : 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_seq; i += kOrderThreads) {
+    const int mine = len[i];
+    int rank = 0;
+    for (int j = 0; j < n_seq; ++j) rank += (len[j] > mine) || (len[j] == mine && j < i);
+    order[rank] = i;
+  }
+}
+
+}  // namespace
+
+size_t chunk_tc_workspace_bytes(int n_seq, int, int) {
+  return n_seq > 1 && n_seq <= kMaxOrdered ? static_cast<size_t>(n_seq) * sizeof(int) : 0;
+}
 
 // Chunk length of the tensor-core kernel: 32-row chunks keep two CTAs resident per SM, 64-row chunks
 // do more work per barrier.  FRWKV_PREFILL_CHUNK=32|64 overrides the default (tuning / test hook).
@@ -34,13 +65,25 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
                     float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
                     cudaStream_t stream) {
+  (void)max_seqlen;
+  const int32_t* order = nullptr;
+  const size_t need = chunk_tc_workspace_bytes(n_seq, total_tokens, heads);
+  if (need > 0 && workspace != nullptr) {  // no scratch given: natural order
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 3) != 0)
+      return fail(FRWKV_ERR_WORKSPACE, "wkv7_prefill: workspace of %zu bytes (4-byte aligned) needed, got %zu", need,
+                  workspace_bytes);
+    sequence_order_kernel<<<1, kOrderThreads, 0, stream>>>(cu, status, n_seq, static_cast<int*>(workspace));
+    const int rc = check_launch("sequence_order_kernel");
+    if (rc != FRWKV_OK) return rc;
+    order = static_cast<const int32_t*>(workspace);
+  }
   int chunk = 32;
   if (const char* e = std::getenv("FRWKV_PREFILL_CHUNK")) chunk = std::atoi(e);
   if (chunk == 32)
     return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                             io_dtype, decay_mode, scale, error_flag, stream);
+                             io_dtype, decay_mode, scale, order, error_flag, stream);
   return launch_chunk64_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                           io_dtype, decay_mode, scale, max_seqlen, workspace, workspace_bytes, error_flag, stream);
+                           io_dtype, decay_mode, scale, order, error_flag, stream);
 }
 
 }  // namespace frwkv

@@ -116,8 +116,10 @@ int frwkv_sm100_wkv7_recurrent(
  * instead of host-built per-chunk metadata.  Same fail-closed rules as above.
  *   strategy   : FRWKV_PREFILL_AUTO picks the tensor-core kernel for 16-bit
  *                tokens and long rows, else the register-streaming recurrence;
- *   workspace  : device scratch of at least
- *                frwkv_sm100_wkv7_prefill_workspace_bytes() bytes (may be NULL if 0);
+ *   workspace  : device scratch of at least frwkv_sm100_wkv7_prefill_workspace_bytes() bytes
+ *                (4 bytes per sequence for batches of 2..2048 sequences), used to hand the
+ *                sequences to the SMs longest first; NULL is accepted and keeps the natural
+ *                order (same results, a longer tail on ragged batches);
  *   error_flag : optional device int32 that the tensor-core kernel sets nonzero if
  *                one of its bounded waits gave up (the output is then invalid). */
 int frwkv_sm100_wkv7_prefill(

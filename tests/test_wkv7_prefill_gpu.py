@@ -196,3 +196,39 @@ def test_native_rl_infctx_symbol_with_host_chunk_metadata():
     y_ref, pool_ref = _oracle(case, f64=True)
     assert torch.equal(working, d["state_pool"])
     assert relative_rmse(y.cpu(), y_ref) <= 7e-3 and relative_rmse(final.cpu(), pool_ref) <= 8e-3
+
+
+def test_longest_first_order_changes_schedule_not_results():
+    """Through the C ABI: with scratch for the longest-first ranking and without it (natural order) the
+    outputs are bit-identical, and scratch that is too small is refused without launching."""
+    from flashrwkv2_b200 import _lib
+
+    lib = _lib.load()
+    case = _random_case((5, 200, 33, 64, 1, 97), 2, torch.bfloat16, seed=51, slots=[3, 0, 5, 1, 4, 2])
+    d = _to_dev(case)
+    n, total, heads = 6, sum((5, 200, 33, 64, 1, 97)), 2
+    need = lib.frwkv_sm100_wkv7_prefill_workspace_bytes(n, total, heads)
+    assert need == n * 4 and lib.frwkv_sm100_wkv7_prefill_workspace_bytes(1, 64, 2) == 0
+    stream = torch.cuda.current_stream().cuda_stream
+    results = []
+    for ws_bytes in (0, need):
+        pool = d["state_pool"].clone()
+        y = torch.empty_like(d["v"])
+        ws = torch.full((max(ws_bytes, 4),), 255, dtype=torch.uint8, device=DEV)
+        rc = lib.frwkv_sm100_wkv7_prefill(
+            d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, pool.data_ptr(),
+            *(d[n_].data_ptr() for n_ in TOKEN_NAMES), 0, y.data_ptr(), 0, n, total, heads, _lib.IO_BF16,
+            _lib.DECAY_RETENTION, 1.0, 200, _lib.PREFILL_CHUNK_TC, ws.data_ptr() if ws_bytes else 0, ws_bytes, 0, stream)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        if ws_bytes:
+            assert ws[:need].view(torch.int32).cpu().tolist() == [1, 5, 3, 2, 0, 4]  # lengths 200,97,64,33,5,1
+        results.append((y.clone(), pool))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    y_ref, pool_ref = _oracle(case, f64=True)
+    assert relative_rmse(results[1][0].cpu(), y_ref) <= 7e-3
+    rc = lib.frwkv_sm100_wkv7_prefill(
+        d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, d["state_pool"].data_ptr(),
+        *(d[n_].data_ptr() for n_ in TOKEN_NAMES), 0, y.data_ptr(), 0, n, total, heads, _lib.IO_BF16,
+        _lib.DECAY_RETENTION, 1.0, 200, _lib.PREFILL_CHUNK_TC, ws.data_ptr(), 8, 0, stream)
+    assert rc != 0 and "workspace" in _lib.last_error()
