@@ -22,7 +22,10 @@
 namespace frwkv {
 namespace {
 
-constexpr int kWarpsPerCta = 4;
+#ifndef FRWKV_WARPS_PER_CTA
+#define FRWKV_WARPS_PER_CTA 4
+#endif
+constexpr int kWarpsPerCta = FRWKV_WARPS_PER_CTA;
 
 template <typename io_t, int N> struct RowVals {  // N consecutive token-dtype values, kept packed
   static constexpr int kBytes = N * sizeof(io_t);
@@ -102,6 +105,13 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
   constexpr int RPL = kHeadDim / GROUPS;   // key rows per lane
   const int lane = threadIdx.x & 31;
   const long long warp = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+
+  // Programmatic dependent launch: this grid may be scheduled while the previous kernel of the stream
+  // drains (its launch latency and ramp are hidden), but nothing is read before that kernel has
+  // completed and its writes are visible -- the state pool is updated in place from step to step.
+  // Without the launch attribute both instructions do nothing.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (p.status != nullptr && p.status[0] != 0) {
     fill_output_nan(static_cast<io_t*>(p.y), p.y_f32,
@@ -216,16 +226,30 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
   for (int i = 0; i < RPL; ++i) __stcs(reinterpret_cast<float4*>(sbase + i * kHeadDim), S[i]);
 }
 
+// FRWKV_PDL=0 turns programmatic dependent launch off (tuning / debugging hook).
+inline bool pdl_enabled() {
+  const char* e = std::getenv("FRWKV_PDL");
+  return e == nullptr || std::atoi(e) != 0;
+}
+
 template <typename io_t, int PARTS, bool PREFETCH>
 int launch(const RecurrentParams& p, bool logits, cudaStream_t stream) {
   const long long warps = static_cast<long long>(p.n_seq) * p.heads * PARTS;
   const long long ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
   if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "recurrent: too many (sequence, head) pairs");
-  const unsigned grid = static_cast<unsigned>(ctas);
-  if (logits)
-    wkv7_recurrent_stream_kernel<io_t, PARTS, true, PREFETCH><<<grid, kWarpsPerCta * 32, 0, stream>>>(p);
-  else
-    wkv7_recurrent_stream_kernel<io_t, PARTS, false, PREFETCH><<<grid, kWarpsPerCta * 32, 0, stream>>>(p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(ctas));
+  config.blockDim = dim3(kWarpsPerCta * 32);
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  auto kernel = logits ? wkv7_recurrent_stream_kernel<io_t, PARTS, true, PREFETCH>
+                       : wkv7_recurrent_stream_kernel<io_t, PARTS, false, PREFETCH>;
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, p);
+  if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent_stream_kernel: %s", cudaGetErrorString(err));
   return check_launch("wkv7_recurrent_stream_kernel");
 }
 
