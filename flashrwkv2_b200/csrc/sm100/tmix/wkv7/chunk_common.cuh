@@ -40,6 +40,7 @@ struct ChunkParams {
   int n_seq, total_tokens, heads;
   float scale;
   const int* order;  // CTA rank -> sequence, longest first (nullptr: natural order)
+  int len_from;      // > 0: only sequences at least this long (shorter ones go to the recurrence kernel)
 };
 
 struct Maps {

@@ -91,7 +91,7 @@ wkv7_chunk_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   const int seq = p.order != nullptr ? p.order[rank] : rank;
   if (seq >= active || seq < 0 || seq >= p.n_seq) return;
   const int t_begin = p.cu[seq], len = p.cu[seq + 1] - t_begin;
-  if (len <= 0) return;
+  if (len <= 0 || len < p.len_from) return;
   const int n_chunks = (len + kChunk - 1) / kChunk;
   const int slot = p.slots[seq];
 
@@ -647,12 +647,12 @@ int launch_typed(const ChunkParams& p, const Maps& maps, bool logits, cudaStream
 int launch_chunk64_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                     const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                    float scale, const int32_t* order, int32_t* error_flag, cudaStream_t stream) {
+                    float scale, const int32_t* order, int len_from, int32_t* error_flag, cudaStream_t stream) {
   const bool bf16 = io_dtype == FRWKV_IO_BF16;
   Maps maps;
   const int map_rc = make_maps(&maps, r, w, k, v, a, b, total_tokens, heads, bf16, kChunk);
   if (map_rc != FRWKV_OK) return map_rc;
-  ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order};
+  ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from};
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
   if (bf16) return launch_typed<__nv_bfloat16>(p, maps, logits, stream);
   return launch_typed<__half>(p, maps, logits, stream);

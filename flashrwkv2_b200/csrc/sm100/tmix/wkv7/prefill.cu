@@ -14,15 +14,15 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
                             const void* r, const void* w, const void* k, const void* v, const void* a,
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
-                            int max_seqlen, int parts_override, cudaStream_t stream);
+                            int max_seqlen, int parts_override, int len_below, cudaStream_t stream);
 int launch_chunk64_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, const int32_t* order, int32_t* error_flag, cudaStream_t stream);
+                      float scale, const int32_t* order, int len_from, int32_t* error_flag, cudaStream_t stream);
 int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, const int32_t* order, int32_t* error_flag, cudaStream_t stream);
+                      float scale, const int32_t* order, int len_from, int32_t* error_flag, cudaStream_t stream);
 
 namespace {
 
@@ -32,6 +32,7 @@ namespace {
 // one small kernel (rank of i = number of sequences that are longer, ties by index) writing
 // order[rank] = i into caller-provided scratch; batches above kMaxOrdered sequences keep their natural
 // order (their tail is negligible and an all-pairs ranking would not be).
+constexpr int kShortRow = 16;  // rows shorter than this go to the recurrence kernel under AUTO
 constexpr int kMaxOrdered = 2048;
 constexpr int kOrderThreads = 1024;
 
@@ -63,8 +64,8 @@ size_t chunk_tc_workspace_bytes(int n_seq, int, int) {
 int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                     const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                    float scale, int max_seqlen, void* workspace, size_t workspace_bytes, int32_t* error_flag,
-                    cudaStream_t stream) {
+                    float scale, int max_seqlen, int len_from, void* workspace, size_t workspace_bytes,
+                    int32_t* error_flag, cudaStream_t stream) {
   (void)max_seqlen;
   const int32_t* order = nullptr;
   const size_t need = chunk_tc_workspace_bytes(n_seq, total_tokens, heads);
@@ -81,9 +82,9 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
   if (const char* e = std::getenv("FRWKV_PREFILL_CHUNK")) chunk = std::atoi(e);
   if (chunk == 32)
     return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                             io_dtype, decay_mode, scale, order, error_flag, stream);
+                             io_dtype, decay_mode, scale, order, len_from, error_flag, stream);
   return launch_chunk64_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                           io_dtype, decay_mode, scale, order, error_flag, stream);
+                           io_dtype, decay_mode, scale, order, len_from, error_flag, stream);
 }
 
 }  // namespace frwkv
@@ -104,20 +105,30 @@ extern "C" int frwkv_sm100_wkv7_prefill(
   if (rc != FRWKV_OK) return rc;
   if (strategy != FRWKV_PREFILL_AUTO && strategy != FRWKV_PREFILL_RECURRENT && strategy != FRWKV_PREFILL_CHUNK_TC)
     return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: unknown strategy %d", strategy);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (strategy == FRWKV_PREFILL_AUTO) {
-    // fp32 tokens ask for 1e-5 agreement: that is the CUDA-core recurrence.  Rows of a
-    // few tokens gain nothing from 64-row chunks.
-    const bool tc = io_dtype != FRWKV_IO_FP32 && (max_seqlen <= 0 || max_seqlen >= 16);
-    strategy = tc ? FRWKV_PREFILL_CHUNK_TC : FRWKV_PREFILL_RECURRENT;
+    // fp32 tokens ask for 1e-5 agreement: that is the CUDA-core recurrence.  Rows of a few tokens gain
+    // nothing from 32-row chunks either.  A batch that may hold both kinds (continuous batching: decode
+    // rows next to a prompt) is split by length: two launches, each kernel skipping the other's rows.
+    if (io_dtype == FRWKV_IO_FP32 || (max_seqlen > 0 && max_seqlen < kShortRow))
+      strategy = FRWKV_PREFILL_RECURRENT;
+    else {
+      rc = launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
+                                   n_seq, total_tokens, heads, io_dtype, decay_mode, scale, kShortRow - 1, 0,
+                                   kShortRow, s);
+      if (rc != FRWKV_OK) return rc;
+      return launch_chunk_tc(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32, n_seq,
+                             total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, kShortRow, workspace,
+                             workspace_bytes, error_flag, s);
+    }
   }
   if (strategy == FRWKV_PREFILL_CHUNK_TC) {
     if (io_dtype == FRWKV_IO_FP32)
       return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_prefill: the tensor-core chunk kernel takes float16 or bfloat16 tokens");
     return launch_chunk_tc(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32, n_seq,
-                           total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, workspace,
-                           workspace_bytes, error_flag, static_cast<cudaStream_t>(stream));
+                           total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, workspace,
+                           workspace_bytes, error_flag, s);
   }
   return launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
-                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0,
-                                 static_cast<cudaStream_t>(stream));
+                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0, s);
 }

@@ -95,6 +95,7 @@ struct RecurrentParams {
   float* y_f32;
   int n_seq, total_tokens, heads;
   float scale;
+  int len_below;  // > 0: only sequences shorter than this (the rest belongs to another kernel of the same call)
 };
 
 template <typename io_t, int PARTS, bool LOGITS, bool PREFETCH>
@@ -128,6 +129,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
   if (seq >= active || seq >= p.n_seq) return;
 
   const int t_lo = p.cu[seq], t_hi = p.cu[seq + 1];
+  if (p.len_below > 0 && t_hi - t_lo >= p.len_below) return;
   const int slot = p.slots[seq];
   const int group = lane / LPR;
   const int col = part * COLS + (lane % LPR) * 4;
@@ -297,8 +299,9 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
                             const void* r, const void* w, const void* k, const void* v, const void* a,
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
-                            int max_seqlen, int parts_override, cudaStream_t stream) {
-  RecurrentParams p{cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads, scale};
+                            int max_seqlen, int parts_override, int len_below, cudaStream_t stream) {
+  RecurrentParams p{cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads, scale,
+                    len_below};
   // Launch shape.  Decode (one token per row): the state is loaded, used once and stored,
   // so all that matters is bytes in flight; two column parts per pair keep every access a
   // full 128-byte line.  Long rows are a latency-bound token loop: thinner warps (more of
@@ -333,6 +336,6 @@ extern "C" int frwkv_sm100_wkv7_recurrent(
                                 y, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
   if (rc != FRWKV_OK) return rc;
   return launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
-                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0,
+                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0,
                                  static_cast<cudaStream_t>(stream));
 }

@@ -232,3 +232,17 @@ def test_longest_first_order_changes_schedule_not_results():
         *(d[n_].data_ptr() for n_ in TOKEN_NAMES), 0, y.data_ptr(), 0, n, total, heads, _lib.IO_BF16,
         _lib.DECAY_RETENTION, 1.0, 200, _lib.PREFILL_CHUNK_TC, ws.data_ptr(), 8, 0, stream)
     assert rc != 0 and "workspace" in _lib.last_error()
+
+
+def test_auto_strategy_splits_a_mixed_batch_by_length():
+    """Decode-like rows next to prompts (continuous batching): under "auto" rows shorter than 16 tokens go to
+    the recurrence kernel and the rest to the tensor-core kernel, in one call; every row must be right."""
+    lengths = (1, 1, 40, 1, 200, 3, 15, 16, 1, 33)
+    case = _random_case(lengths, 3, torch.bfloat16, seed=61, slots=[9, 0, 8, 1, 7, 2, 6, 3, 5, 4], pool_slots=11)
+    y, y32, pool = _run_op(case, op="prefill", strategy="auto")
+    _check(case, y, y32, pool)
+    # the short rows are computed in fp32 by the recurrence kernel: they meet its 1e-5 gate
+    y_ref, _ = _oracle(case, f64=True)
+    cu = case["cu_seqlens"].tolist()
+    short_rows = torch.cat([torch.arange(cu[i], cu[i + 1]) for i, n in enumerate(lengths) if n < 16])
+    assert max_err_over_rms(y32[short_rows], y_ref[short_rows]) <= 1e-5
