@@ -43,14 +43,15 @@ constexpr uint32_t kOffMisc = kOffV + 2 * kTileV;     // gamma_L[64], group sums
 constexpr uint32_t kMiscBytes = 64 * 4 + kWarps * 64 * 4 + 64;
 constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 128;
 static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM's shared memory");
-// fp32 scratch of the 32x32 inverse, aliased onto [At; Rt] (dead once P and Q are complete), so that
-// the TMA staging area is free as soon as stage A is done and the next chunk's load can start then
+// fp32 scratch of the 32x32 inverse, aliased onto the TMA staging area (free after stage A; the next
+// chunk's load is issued once the inverse is done).  [At; Rt] cannot host it: Q = [At; Rt] S0 is still
+// being computed while P is read back.
 constexpr int kInvLd = 36;
-constexpr uint32_t kOffAb = kOffX1;                    // A_ab [32][36]
+constexpr uint32_t kOffAb = kOffRaw;                   // A_ab [32][36]
 constexpr uint32_t kOffTi = kOffAb + 32 * kInvLd * 4;  // T    [32][36]
 constexpr int kMbLd = 17;
 constexpr uint32_t kOffMb = kOffTi + 32 * kInvLd * 4;  // block product [16][17]
-static_assert(kOffMb + 16 * kMbLd * 4 <= kOffX2, "inverse scratch must fit in the [At; Rt] tile");
+static_assert(kOffMb + 16 * kMbLd * 4 <= kOffX1, "inverse scratch must fit in the staging area");
 
 // ---- TMEM map (columns) --------------------------------------------------------------------
 constexpr uint32_t kTmemCols = 256;
@@ -307,15 +308,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     __syncthreads();
 
     FRWKV_PHASE(1)
-    // the staging area has been consumed: start the next chunk's load (a thread other than the MMA issuer)
-    if (tid == 32 && c + 1 < n_chunks) issue_tma(c + 1);
-    if (c + 1 < n_chunks) tma_in_flight = true;
     // ================= P = X1 X2^T ; Q = X1 S0 =================
     if (tid == 0) {
       tcgen05_fence_after_sync();
       issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
+      mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back; the commit after the
+                            // [A_ak; A_rk] V product covers it (commits track every earlier MMA)
       issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
-      mma_commit(bar_mma);
     }
     {
       const bool ok = mbar_wait(bar_mma, mma_uses & 1);
@@ -406,27 +405,27 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
       {
         const int rr = tid >> 4, cc = tid & 15;
-        float acc = 0.0f;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four independent partial sums: no 16-deep FMA chain
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4) {
           const float4 av = *reinterpret_cast<const float4*>(ab + (16 + rr) * kInvLd + 4 * s4);
-          acc = fmaf(av.x, ti[(4 * s4 + 0) * kInvLd + cc], acc);
-          acc = fmaf(av.y, ti[(4 * s4 + 1) * kInvLd + cc], acc);
-          acc = fmaf(av.z, ti[(4 * s4 + 2) * kInvLd + cc], acc);
-          acc = fmaf(av.w, ti[(4 * s4 + 3) * kInvLd + cc], acc);
+          acc[0] = fmaf(av.x, ti[(4 * s4 + 0) * kInvLd + cc], acc[0]);
+          acc[1] = fmaf(av.y, ti[(4 * s4 + 1) * kInvLd + cc], acc[1]);
+          acc[2] = fmaf(av.z, ti[(4 * s4 + 2) * kInvLd + cc], acc[2]);
+          acc[3] = fmaf(av.w, ti[(4 * s4 + 3) * kInvLd + cc], acc[3]);
         }
-        mb[rr * kMbLd + cc] = acc;
+        mb[rr * kMbLd + cc] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
         __syncthreads();
-        acc = 0.0f;
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4) {
           const float4 dv = *reinterpret_cast<const float4*>(ti + (16 + rr) * kInvLd + 16 + 4 * s4);
-          acc = fmaf(dv.x, mb[(4 * s4 + 0) * kMbLd + cc], acc);
-          acc = fmaf(dv.y, mb[(4 * s4 + 1) * kMbLd + cc], acc);
-          acc = fmaf(dv.z, mb[(4 * s4 + 2) * kMbLd + cc], acc);
-          acc = fmaf(dv.w, mb[(4 * s4 + 3) * kMbLd + cc], acc);
+          acc[0] = fmaf(dv.x, mb[(4 * s4 + 0) * kMbLd + cc], acc[0]);
+          acc[1] = fmaf(dv.y, mb[(4 * s4 + 1) * kMbLd + cc], acc[1]);
+          acc[2] = fmaf(dv.z, mb[(4 * s4 + 2) * kMbLd + cc], acc[2]);
+          acc[3] = fmaf(dv.w, mb[(4 * s4 + 3) * kMbLd + cc], acc[3]);
         }
-        ti[(16 + rr) * kInvLd + cc] = acc;
+        ti[(16 + rr) * kInvLd + cc] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
       }
       __syncthreads();
       FRWKV_PHASE(11)
@@ -458,6 +457,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
     FRWKV_PHASE(5)
     // ================= U = T W  (rows 32..63 of this product are unused) =================
+    // the staging area (and the inverse scratch in it) is free: start the next chunk's load, from a thread
+    // other than the MMA issuer
+    if (tid == 32 && c + 1 < n_chunks) issue_tma(c + 1);
+    if (c + 1 < n_chunks) tma_in_flight = true;
     if (tid == 0) {
       tcgen05_fence_after_sync();
       issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
