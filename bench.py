@@ -16,11 +16,12 @@ Keys of the JSON line:
   roofline   the decode kernel's algorithmic bytes per launch / its average duration, against
              the measured HBM copy bandwidth;
   cpu_baseline  the port of the reference's fp32 PyTorch recurrence on the host cores;
+  gpu_baseline  (extra) the reference's own CUDA kernels, built unmodified for sm_100, on this GPU;
   prefill    (extra) the same figures for the dense prefill workload (8 x 4096 tokens, H=32).
 
 ``--impl reference`` times the reference's CPU implementation of the path (its fp32 PyTorch
-token loop, restated in oracle/wkv7_oracle.py: the reference's native kernels do not build
-for sm_100 and its CPU path is that loop) on the same workload.
+token loop, restated in oracle/wkv7_oracle.py: its package refuses to import on capability
+10.x and its CPU path is that loop) on the same workload.
 """
 
 from __future__ import annotations
@@ -304,6 +305,10 @@ def run_ours(args, rank, local_rank, world):
                 line["prefill"] = prefill_extra(lib, _lib, device, peaks, stream)
             except RuntimeError as error:  # reported, not hidden
                 line["prefill"] = {"error": str(error)}
+            try:
+                line["gpu_baseline"] = gpu_baseline(device, sets)
+            except RuntimeError as error:
+                line["gpu_baseline"] = {"error": str(error)}
     return line
 
 
@@ -386,6 +391,73 @@ def cpu_baseline(name, wl):
     return {"value": round(value, 1), "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": sample + " (fp32 PyTorch token loop, the reference's CPU path restated)",
             "c_openmp_port": {"value": round(c_value, 1), "cores": c_cores}, "host_cpus": os.cpu_count()}
+
+
+def gpu_baseline(device, decode_sets):
+    """The reference project's own CUDA kernels on this GPU (a baseline, like cpu_baseline): its unmodified
+    recurrent and rl_infctx chunk-forward sources built for sm_100 into oracle/_ref (oracle/build_ref.py), called
+    through the reference's native symbols.  Decode: the headline workload, ticket prepared once, rotating sets.
+    Prefill: the dense 8 x 4096 workload through the recurrent operator (what the reference's inference path runs
+    for T > 1) and through the rl_infctx chunk operator (chunk 64; clones and workspaces included, as its API does).
+    The reference has only the logits decay mode; kernel time does not depend on the values."""
+    from flashrwkv2_b200.workloads import make_workload
+    from oracle.build_ref import load_ref
+
+    ref = load_ref()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/_C_ref.so not built (needs a reference checkout at build time)"}
+    out = {"kind": "reference kernels, unmodified sources compiled for sm_100"}
+    names = ("r", "w", "k", "v", "a", "b")
+    # decode
+    tickets, ys = [], []
+    for wl in decode_sets:
+        t = wl.tensors
+        tickets.append(ref.prepare_tmix_wkv7_recurrent_metadata(t["cu_seqlens"], t["state_indices"], wl.total_tokens,
+                                                                 t["state_pool"].shape[0], 1))
+        ys.append(torch.empty_like(t["v"]))
+
+    def decode_step(i):
+        j = i % len(decode_sets)
+        t = decode_sets[j].tensors
+        ref.tmix_wkv7_recurrent_fp32_from_decay_logits(t["cu_seqlens"], t["state_indices"], t["state_pool"],
+                                                       *(t[n] for n in names), ys[j], 1.0, None, tickets[j], 1)
+
+    for i in range(5):
+        decode_step(i)
+    steps = 200
+    ms = _event_time_ms(decode_step, steps) / steps
+    tokens = decode_sets[0].total_tokens
+    out["decode"] = {"kernel": "wkv_fp32_v2_small_warp_kernel", "tokens_per_s": round(tokens / (ms * 1e-3), 1),
+                     "us_per_step": round(ms * 1e3, 2)}
+    # prefill
+    wl = make_workload("c2", device=device)
+    t = wl.tensors
+    y = torch.empty_like(t["v"])
+    ticket = ref.prepare_tmix_wkv7_recurrent_metadata(t["cu_seqlens"], t["state_indices"], wl.total_tokens,
+                                                      t["state_pool"].shape[0], 4096)
+
+    def recurrent_step(i):
+        ref.tmix_wkv7_recurrent_fp32_from_decay_logits(t["cu_seqlens"], t["state_indices"], t["state_pool"],
+                                                       *(t[n] for n in names), y, 1.0, None, ticket, 4096)
+
+    starts = torch.arange(0, wl.total_tokens, 64, dtype=torch.int32, device=device)
+    meta = (torch.arange(0, wl.n_seq + 1, dtype=torch.int32, device=device) * (4096 // 64), starts, starts + 64)
+
+    def chunk_step(strategy):
+        def step(i):
+            ref.rl_infctx_tmix_wkv7_chunk_fp32io16_forward(*meta, t["state_pool"], *(t[n] for n in names), strategy,
+                                                           1.0, None)
+        return step
+
+    out["prefill"] = {"workload": "c2: prefill N=8 T=4096 H=32 D=64 bf16"}
+    for label, fn in (("recurrent (wkv_fp32_v2_kernel)", recurrent_step),
+                      ("rl_infctx chunk 64, recompute", chunk_step(1)),
+                      ("rl_infctx chunk 64, materialized", chunk_step(0))):
+        for i in range(2):
+            fn(i)
+        ms = _event_time_ms(fn, 5) / 5
+        out["prefill"][label] = {"tokens_per_s": round(wl.total_tokens / (ms * 1e-3), 1), "ms_per_step": round(ms, 4)}
+    return out
 
 
 def run_reference(args, rank, world):

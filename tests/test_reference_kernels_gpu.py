@@ -1,0 +1,136 @@
+"""Drop-in check on a GPU: the product module and a build of the reference project's own CUDA kernels are called
+through the SAME pybind symbols with the SAME device tensors, and must agree.
+
+`oracle/_ref/_C_ref.so` is the reference's unmodified recurrent and rl_infctx chunk-forward sources compiled for
+sm_100 (oracle/build_ref.py; rwkv-rs/FlashRWKV2 csrc/sm120/tmix/wkv7/infer_recurrent_fp32io16_forward_varlen.{cpp,cu},
+rl_infctx_chunk_fp32io16_forward.{cpp,cu}).  It exists only where a reference checkout was present at build time, so
+every test here skips without it.  Gates: 1e-5 max|d|/RMS between the two fp32 recurrences (same arithmetic, other
+summation order), the 16-bit y within one unit in the last place; 5e-3 max|d|/RMS for the tensor-core chunk kernel.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+from conftest import TOKEN_NAMES
+from test_wkv7_recurrent_gpu import _random_case, _to_dev
+
+from oracle.build_ref import load_ref
+from oracle.wkv7_oracle import max_err_over_rms
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ref():
+    module = load_ref()
+    if module is None:
+        pytest.skip("oracle/_ref/_C_ref.so was not built (no reference checkout at build time)")
+    return module
+
+
+@pytest.fixture(scope="module")
+def ours():
+    import flashrwkv2_b200
+
+    assert flashrwkv2_b200._C is not None and flashrwkv2_b200._C.__file__.endswith(".so")
+    return flashrwkv2_b200._C
+
+
+def _recurrent(module, d, *, ticket: bool, max_seqlen: int):
+    pool = d["state_pool"].clone()
+    y = torch.empty_like(d["v"])
+    validated = None
+    if ticket:
+        validated = module.prepare_tmix_wkv7_recurrent_metadata(d["cu_seqlens"], d["state_indices"],
+                                                                d["r"].shape[0], pool.shape[0], max_seqlen)
+    module.tmix_wkv7_recurrent_fp32_from_decay_logits(d["cu_seqlens"], d["state_indices"], pool,
+                                                      *(d[n] for n in TOKEN_NAMES), y, float(d["scale"]),
+                                                      d["decay_bias"], validated, max_seqlen)
+    torch.cuda.synchronize()
+    return y.float().cpu(), pool.cpu()
+
+
+def _one_ulp(y_a, y_b, dtype):
+    """16-bit outputs of two fp32 computations may round to neighbouring values."""
+    eps = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    tol = eps * torch.maximum(y_a.abs(), y_b.abs()) + 1e-6
+    return bool(((y_a - y_b).abs() <= tol).all())
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("bias", (False, True))
+def test_decode_step_matches_the_reference_kernel(ref, ours, dtype, bias):
+    case = _random_case((1,) * 48, 4, dtype, seed=71, retention=False, bias=bias,
+                        slots=list(reversed(range(48))), pool_slots=50)
+    case["scale"] = 0.75
+    d = _to_dev(case)
+    d["scale"] = case["scale"]
+    y_ref, pool_ref = _recurrent(ref, d, ticket=True, max_seqlen=1)
+    y, pool = _recurrent(ours, d, ticket=True, max_seqlen=1)
+    assert max_err_over_rms(pool, pool_ref) <= 1e-5
+    assert _one_ulp(y, y_ref, dtype)
+    assert torch.equal(pool[48:], pool_ref[48:])  # slots outside state_indices: untouched by both
+
+
+@pytest.mark.parametrize("ticket", (False, True))
+def test_ragged_recurrence_matches_the_reference_kernel(ref, ours, ticket):
+    lengths = (5, 1, 33, 64, 2, 17)
+    case = _random_case(lengths, 3, torch.bfloat16, seed=72, retention=False, bias=True)
+    d = _to_dev(case)
+    d["scale"] = 1.0
+    y_ref, pool_ref = _recurrent(ref, d, ticket=ticket, max_seqlen=max(lengths))
+    y, pool = _recurrent(ours, d, ticket=ticket, max_seqlen=max(lengths))
+    assert max_err_over_rms(pool, pool_ref) <= 1e-5
+    assert _one_ulp(y, y_ref, torch.bfloat16)
+
+
+def test_invalid_metadata_is_rejected_like_the_reference(ref, ours):
+    """Duplicate slots: preparing a ticket raises ("unique"); the un-ticketed native call validates on the
+    device and fails closed, i.e. y is all NaN and the pool is untouched, in both modules."""
+    case = _random_case((2, 2), 2, torch.bfloat16, seed=73, retention=False)
+    d = _to_dev(case)
+    d["scale"] = 1.0
+    d["state_indices"] = torch.tensor([1, 1], dtype=torch.int32, device=DEV)
+    for module in (ref, ours):
+        with pytest.raises(RuntimeError, match="unique"):
+            module.prepare_tmix_wkv7_recurrent_metadata(d["cu_seqlens"], d["state_indices"], 4, 2, 2)
+        y, pool = _recurrent(module, d, ticket=False, max_seqlen=2)
+        assert bool(torch.isnan(y).all())
+        assert torch.equal(pool, case["state_pool"])
+
+
+def _chunk_metadata(lengths, chunk):
+    offsets, starts, ends, begin = [0], [], [], 0
+    for length in lengths:
+        for s in range(begin, begin + length, chunk):
+            starts.append(s)
+            ends.append(min(s + chunk, begin + length))
+        offsets.append(len(starts))
+        begin += length
+    return tuple(torch.tensor(x, dtype=torch.int32, device=DEV) for x in (offsets, starts, ends))
+
+
+@pytest.mark.parametrize("strategy", (0, 1))
+@pytest.mark.parametrize("chunk", (16, 64))
+def test_chunk_forward_matches_the_reference_kernels(ref, ours, strategy, chunk):
+    lengths = (130, 64, 37, 256)
+    case = _random_case(lengths, 2, torch.bfloat16, seed=74 + chunk, retention=False, bias=True)
+    d = _to_dev(case)
+    meta = _chunk_metadata(lengths, chunk)
+    results = []
+    for module in (ref, ours):
+        state = d["state_pool"].clone()
+        y, final = module.rl_infctx_tmix_wkv7_chunk_fp32io16_forward(*meta, state, *(d[n] for n in TOKEN_NAMES),
+                                                                     strategy, 1.0, d["decay_bias"])
+        torch.cuda.synchronize()
+        assert torch.equal(state, d["state_pool"]), "the caller's state must not be modified"
+        results.append((y.float().cpu(), final.cpu()))
+    (y_ref, s_ref), (y, s) = results
+    assert max_err_over_rms(s, s_ref) <= 5e-3
+    rms = float((y_ref ** 2).mean().sqrt())
+    # both y are bf16: the 5e-3 gate plus one rounding step of the larger value
+    assert bool(((y - y_ref).abs() <= 5e-3 * rms + 2.0 ** -7 * torch.maximum(y.abs(), y_ref.abs())).all())
+    assert float(((y - y_ref) ** 2).mean().sqrt() / (y_ref ** 2).mean().sqrt()) <= 7e-3
