@@ -134,3 +134,47 @@ def test_chunk_forward_matches_the_reference_kernels(ref, ours, strategy, chunk)
     # both y are bf16: the 5e-3 gate plus one rounding step of the larger value
     assert bool(((y - y_ref).abs() <= 5e-3 * rms + 2.0 ** -7 * torch.maximum(y.abs(), y_ref.abs())).all())
     assert float(((y - y_ref) ** 2).mean().sqrt() / (y_ref ** 2).mean().sqrt()) <= 7e-3
+
+
+def _device_rms(x):
+    return float(x.float().pow(2).mean().sqrt())
+
+
+@pytest.mark.parametrize("name", ("c1", "c2", "c3", "c4_decode", "c4_prefill"))
+def test_full_size_configurations_match_the_reference_kernels(ref, ours, name):
+    """Every benchmark configuration at its full size (the CPU oracle cannot reach these): the product's operator
+    (decode kernel for T=1, tensor-core chunk kernel otherwise) against the reference's recurrent kernel, logits
+    decay mode, inputs generated on the device with the benchmark's distributions."""
+    from flashrwkv2_b200.workloads import make_workload
+
+    wl = make_workload(name, device=DEV)
+    t = wl.tensors
+    g = torch.Generator(device=DEV).manual_seed(wl.seed + 100)
+    logits = torch.empty_like(t["w"])
+    for lo in range(0, wl.total_tokens, 65536):  # bounded temporaries
+        hi = min(wl.total_tokens, lo + 65536)
+        logits[lo:hi] = (torch.randn((hi - lo, wl.heads, 64), generator=g, device=DEV) * 3.5).to(logits.dtype)
+    tokens = (t["r"], logits, t["k"], t["v"], t["a"], t["b"])
+    max_len = max(wl.lengths)
+    outs = []
+    for module in (ref, ours):
+        pool = t["state_pool"].clone()
+        y = torch.empty_like(t["v"])
+        ticket = module.prepare_tmix_wkv7_recurrent_metadata(t["cu_seqlens"], t["state_indices"], wl.total_tokens,
+                                                             pool.shape[0], max_len)
+        if module is ours and max_len > 1:
+            module.tmix_wkv7_prefill_fp32(t["cu_seqlens"], t["state_indices"], pool, *tokens, y, 1.0, None, ticket,
+                                          max_len, "logits", "auto")
+        else:
+            module.tmix_wkv7_recurrent_fp32_from_decay_logits(t["cu_seqlens"], t["state_indices"], pool, *tokens, y,
+                                                              1.0, None, ticket, max_len)
+        torch.cuda.synchronize()
+        outs.append((y, pool))
+    (y_ref, s_ref), (y, s) = outs
+    gate = 1e-5 if max_len == 1 else 5e-3
+    assert float((s - s_ref).abs().max()) <= gate * _device_rms(s_ref)
+    rms = _device_rms(y_ref[: 1 << 16])
+    for lo in range(0, wl.total_tokens, 1 << 16):
+        a, b = y[lo:lo + (1 << 16)].float(), y_ref[lo:lo + (1 << 16)].float()
+        tol = gate * rms + 2.0 ** -7 * torch.maximum(a.abs(), b.abs())  # one bf16 rounding step on top of the gate
+        assert bool(((a - b).abs() <= tol).all()), (name, lo)
