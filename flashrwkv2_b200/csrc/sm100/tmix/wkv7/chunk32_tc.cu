@@ -23,6 +23,7 @@ using namespace chunk;
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kChunk = 32;
+constexpr int kIssuerQ = 96;  // lane 0 of a warp with slack in the inverse phase
 
 // ---- shared-memory map (bytes) -------------------------------------------------------------
 constexpr uint32_t kStride64 = 8 * 128 + 16;  // stride between 16-byte chunks of a 64-row tile (padded)
@@ -312,8 +313,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     if (tid == 0) {
       tcgen05_fence_after_sync();
       issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
-      mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back; the commit after the
-                            // [A_ak; A_rk] V product covers it (commits track every earlier MMA)
+      mma_commit(bar_mma);  // P only
+    }
+    // Q = X1 S0 executes while P is read back.  A second thread issues everything that accumulates into Q
+    // (this product and [A_ak; A_rk] V) and commits it: an issuing thread stalls while the MMA queue is
+    // full, and a commit tracks the MMAs of its own thread only.
+    if (tid == kIssuerQ) {
+      tcgen05_fence_after_sync();
       issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
     }
     {
@@ -360,7 +366,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
     FRWKV_PHASE(3)
     // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
-    if (tid == 0) {
+    if (tid == kIssuerQ) {
       tcgen05_fence_after_sync();
       issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
       mma_commit(bar_mma);
