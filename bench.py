@@ -233,10 +233,11 @@ def run_ours(args, rank, local_rank, world):
     if args.no_e2e or h2d > 8 * 2**30:  # bound pinned host memory on shared boxes
         clocks = sampler.stop()
     else:
-        # the caller's six token tensors live in one pinned host block -> one host->device copy per step;
-        # y goes back on a second stream so that it overlaps the next step's upload (PCIe is full duplex)
+        # the caller's six token tensors live in one pinned host block -> one host->device copy per step.
+        # Two streams, as a serving loop would run it: step i+1's upload overlaps step i's kernel and the
+        # download of its y (PCIe is full duplex); every step still uploads its inputs and downloads its result.
         host = torch.stack([src[n].cpu() for n in "rwkvab"]).pin_memory()
-        dev_in = torch.empty_like(host, device=device)
+        dev_in = [torch.empty_like(host, device=device) for _ in range(2)]
         y_host = [torch.empty(src["v"].shape, dtype=src["v"].dtype).pin_memory() for _ in range(2)]
         pool = src["state_pool"]
         cu, slots = src["cu_seqlens"], src["state_indices"]
@@ -245,22 +246,27 @@ def run_ours(args, rank, local_rank, world):
         op = (ops.infer_tmix_wkv7_recurrent_fp32io16_forward_varlen if is_decode
               else ops.infer_tmix_wkv7_prefill_fp32io16_forward_varlen)
         main_stream = torch.cuda.current_stream()
-        copy_stream = torch.cuda.Stream()
+        up_stream = torch.cuda.Stream()
         uploaded = [torch.cuda.Event(), torch.cuda.Event()]
+        consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        for ev in consumed:
+            ev.record(main_stream)
 
         def e2e_step(i):
-            dev_in.copy_(host, non_blocking=True)
-            out = op(dev_in[0], dev_in[1], dev_in[2], dev_in[3], dev_in[4], dev_in[5], state_pool=pool,
-                     cu_seqlens=cu, state_indices=slots, validated_metadata=ticket, decay_mode="retention")
-            done = uploaded[i % 2]
-            done.record(main_stream)
-            copy_stream.wait_event(done)
-            with torch.cuda.stream(copy_stream):
-                y_host[i % 2].copy_(out, non_blocking=True)
-            out.record_stream(copy_stream)
+            j = i % 2
+            up_stream.wait_event(consumed[j])  # the kernel that last read this input buffer has finished
+            with torch.cuda.stream(up_stream):
+                dev_in[j].copy_(host, non_blocking=True)
+                uploaded[j].record(up_stream)
+            main_stream.wait_event(uploaded[j])
+            d = dev_in[j]
+            out = op(d[0], d[1], d[2], d[3], d[4], d[5], state_pool=pool, cu_seqlens=cu, state_indices=slots,
+                     validated_metadata=ticket, decay_mode="retention")
+            consumed[j].record(main_stream)
+            y_host[j].copy_(out, non_blocking=True)
 
         def e2e_finish():
-            main_stream.wait_stream(copy_stream)
+            main_stream.wait_stream(up_stream)
 
         e2e_steps = max(3, min(args.steps, 2000 if is_decode else 20))
         for i in range(min(args.warmup, 10)):
