@@ -141,6 +141,27 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
   };
 
+  // Fragment view of an accumulator block (tmem_ld_frag16): this thread holds rows frow0 and frow0 + 8 of its
+  // quadrant and, of the 32 columns at 32*half, the pairs 8n + 2*fq + {0,1}, n = 0..3.
+  const int fq = lane & 3;
+  const int frow0 = quad * 16 + (lane >> 2);
+  // fragment -> hi/lo operand tile at `tile` (rows = accumulator rows, 16-byte column chunks from `chunk0` on):
+  // one 4-byte store per pair and part; the 32 lanes of a store cover 128 contiguous bytes
+  auto store_operand_frag = [&](uint32_t tile, uint32_t lo_off, int chunk0, const float (&x)[16]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = frow0 + 8 * h;
+      uint8_t* dst = smem + tile + (row >> 3) * kRowGroup + (row & 7) * 16 + fq * 4;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        uint32_t hi, lo;
+        split2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1], hi, lo);
+        *reinterpret_cast<uint32_t*>(dst + (chunk0 + n) * kStride64) = hi;
+        *reinterpret_cast<uint32_t*>(dst + lo_off + (chunk0 + n) * kStride64) = lo;
+      }
+    }
+  };
+
   // ---- initial state: global -> TMEM (fp32) and -> S0 operand tile ----------------------------
   float* state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
   {
@@ -181,6 +202,18 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   // [Bt; Kt] read MN-major: M = key channel, contraction = tile row (Bt rows 0..31, Kt rows 32..63)
   const Operand op_bt = make_operand(sbase + kOffX2, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
   const Operand op_kt = make_operand(sbase + kOffX2 + 4 * kRowGroup, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
+
+  auto rows_to_operand = [&](uint32_t col) {  // accumulator rows 0..31 x 64 columns at `col` -> kOffOp
+    if (quad < 2) {
+      uint32_t regs[16];
+      tmem_ld_frag16(tmem_lane + col + half * 32, regs);
+      tmem_ld_wait();
+      float x[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[i] = __uint_as_float(regs[i]);
+      store_operand_frag(kOffOp, kTileK64, half * 4, x);
+    }
+  };
 
   uint32_t mma_uses = 0;
   bool failed = false;
@@ -334,30 +367,32 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     {
       // accumulator row arow: rows 0..31 belong to At (quadrants 0,1), rows 32..63 to Rt (quadrants 2,3);
       // columns 32*half..: half 0 = products with Bt (A_ab / A_rb), half 1 = with Kt (A_ak / A_rk)
-      uint32_t regs[32];
-      tmem_ld32(tmem_lane + kColP + half * 32, regs);
+      uint32_t regs[16];
+      tmem_ld_frag16(tmem_lane + kColP + half * 32, regs);
       tmem_ld_wait();
-      if (row_lane) {
-        const int t = arow & 31;
+      float vals[16];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = (frow0 + 8 * h) & 31;
         const int limit = quad < 2 ? t : t + 1;  // keep columns s < limit
-        float vals[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) vals[i] = i < limit ? __uint_as_float(regs[i]) : 0.0f;
-        if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
-          float4* dst = reinterpret_cast<float4*>(smem + kOffAb + t * kInvLd * 4);
+        for (int n = 0; n < 4; ++n) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dst[j] = make_float4(vals[4 * j], vals[4 * j + 1], vals[4 * j + 2], vals[4 * j + 3]);
-        } else {
-          // half 1: A_ak -> X3 row t (quad<2), A_rk -> X3 row 32+t (quad>=2); half 0, quad>=2: A_rb -> X4 row 32+t
-          uint8_t* dst = smem + (half == 1 ? kOffX3 : kOffX4) + (arow >> 3) * kRowGroup + (arow & 7) * 16;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 hi, lo;
-            split8(vals + 8 * j, hi, lo);
-            *reinterpret_cast<uint4*>(dst + j * kStride64) = hi;
-            *reinterpret_cast<uint4*>(dst + kTileK32 + j * kStride64) = lo;
-          }
+          for (int e = 0; e < 2; ++e)
+            vals[4 * n + 2 * h + e] = 8 * n + 2 * fq + e < limit ? __uint_as_float(regs[4 * n + 2 * h + e]) : 0.0f;
         }
+      }
+      if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float* dst = reinterpret_cast<float*>(smem + kOffAb) + (frow0 + 8 * h) * kInvLd + 2 * fq;
+#pragma unroll
+          for (int n = 0; n < 4; ++n)
+            *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(vals[4 * n + 2 * h], vals[4 * n + 2 * h + 1]);
+        }
+      } else {
+        // half 1: A_ak -> X3 rows 0..31 (quad<2), A_rk -> X3 rows 32..63; half 0, quad>=2: A_rb -> X4 rows 32..63
+        store_operand_frag(half == 1 ? kOffX3 : kOffX4, kTileK32, 0, vals);
       }
     }
     fence_proxy_async_smem();
@@ -398,12 +433,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       } else {
         w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_uses & 1));
         tcgen05_fence_after_sync();
-        if (w_ready) {
-          uint32_t regs[32];
-          tmem_ld32(tmem_lane + kColQ + half * 32, regs);
-          tmem_ld_wait();
-          if (row_lane) store_operand_row(arow, regs);
-        }
+        if (w_ready) rows_to_operand(kColQ);
       }
       ++mma_uses;
       if (__syncthreads_or(!w_ready)) { failed = true; break; }
@@ -449,14 +479,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
     }
     FRWKV_PHASE(4)
-    auto rows_to_operand = [&](uint32_t col) {  // accumulator rows 0..31 x 64 columns at `col` -> kOffOp
-      if (quad < 2) {
-        uint32_t regs[32];
-        tmem_ld32(tmem_lane + col + half * 32, regs);
-        tmem_ld_wait();
-        if (row_lane) store_operand_row(arow, regs);
-      }
-    };
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
     __syncthreads();
@@ -503,26 +525,23 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     FRWKV_PHASE(8)
     // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
     if (quad >= 2) {
-      uint32_t regs[32];
-      tmem_ld32(tmem_lane + kColQ + half * 32, regs);
+      uint32_t regs[16];
+      tmem_ld_frag16(tmem_lane + kColQ + half * 32, regs);
       tmem_ld_wait();
-      const int t = arow - 32;
-      if (row_lane && t < rows) {
-        const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32;
-        io_t* yp = static_cast<io_t*>(p.y) + out;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          alignas(16) io_t packed[8];
+      for (int h = 0; h < 2; ++h) {
+        const int t = frow0 + 8 * h - 32;
+        if (t < rows) {
+          const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
+          io_t* yp = static_cast<io_t*>(p.y) + out;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) packed[e] = from_f32<io_t>(__uint_as_float(regs[8 * j + e]) * p.scale);
-          *reinterpret_cast<uint4*>(yp + 8 * j) = *reinterpret_cast<const uint4*>(packed);
-        }
-        if (p.y_f32 != nullptr) {
-          float4* yf = reinterpret_cast<float4*>(p.y_f32 + out);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            yf[j] = make_float4(__uint_as_float(regs[4 * j]) * p.scale, __uint_as_float(regs[4 * j + 1]) * p.scale,
-                                __uint_as_float(regs[4 * j + 2]) * p.scale, __uint_as_float(regs[4 * j + 3]) * p.scale);
+          for (int n = 0; n < 4; ++n) {
+            const float y0 = __uint_as_float(regs[4 * n + 2 * h]) * p.scale;
+            const float y1 = __uint_as_float(regs[4 * n + 2 * h + 1]) * p.scale;
+            alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
+            *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
+            if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
+          }
         }
       }
     }
@@ -533,22 +552,28 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
     // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
     {
-      uint32_t regs[32];
-      tmem_ld32(tmem_lane + kColS + half * 32, regs);
+      uint32_t regs[16];
+      tmem_ld_frag16(tmem_lane + kColS + half * 32, regs);
       tmem_ld_wait();
-      const float gl = gamma_l[arow];
+      const float gl[2] = {gamma_l[frow0], gamma_l[frow0 + 8]};
+      float x[16];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) regs[i] = __float_as_uint(__uint_as_float(regs[i]) * gl);
+      for (int i = 0; i < 16; ++i) {
+        x[i] = __uint_as_float(regs[i]) * gl[(i >> 1) & 1];
+        regs[i] = __float_as_uint(x[i]);
+      }
       if (c + 1 < n_chunks) {
-        tmem_st32(tmem_lane + kColS + half * 32, regs);
-        if (row_lane) store_operand_row(arow, regs);
+        tmem_st_frag16(tmem_lane + kColS + half * 32, regs);
+        store_operand_frag(kOffOp, kTileK64, half * 4, x);
         tmem_st_wait();
-      } else if (row_lane) {
-        float4* dst = reinterpret_cast<float4*>(state_g + arow * kHeadDim + half * 32);
+      } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          __stcs(dst + i, make_float4(__uint_as_float(regs[4 * i]), __uint_as_float(regs[4 * i + 1]),
-                                      __uint_as_float(regs[4 * i + 2]), __uint_as_float(regs[4 * i + 3])));
+        for (int h = 0; h < 2; ++h) {
+          float* dst = state_g + (frow0 + 8 * h) * kHeadDim + half * 32 + 2 * fq;
+#pragma unroll
+          for (int n = 0; n < 4; ++n)
+            __stcs(reinterpret_cast<float2*>(dst + 8 * n), make_float2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1]));
+        }
       }
     }
     fence_proxy_async_smem();
