@@ -23,7 +23,6 @@ using namespace chunk;
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kChunk = 32;
-constexpr int kIssuerQ = 96;  // lane 0 of a warp with slack in the inverse phase
 
 // ---- shared-memory map (bytes) -------------------------------------------------------------
 constexpr uint32_t kStride64 = 8 * 128 + 16;  // stride between 16-byte chunks of a 64-row tile (padded)
@@ -217,6 +216,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
   uint32_t mma_uses = 0;
   bool failed = false;
+  bool bad = false;  // this thread saw a bounded wait give up; turned into `failed` at the next CTA barrier
 #ifdef FRWKV_CHUNK_TIMING
   long long phase_t0 = clock64();
 #endif
@@ -343,24 +343,18 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
     FRWKV_PHASE(1)
     // ================= P = X1 X2^T ; Q = X1 S0 =================
+    // One thread issues every MMA, in the order the results are needed: the tensor pipe runs them first in,
+    // first out.  The issuer stalls while the MMA queue is full, so no CTA-wide barrier follows an MMA wait: each
+    // warp goes on as soon as the mbarrier flips, and a wait that gave up is reported at the next barrier.
     if (tid == 0) {
       tcgen05_fence_after_sync();
       issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
-      mma_commit(bar_mma);  // P only
-    }
-    // Q = X1 S0 executes while P is read back.  A second thread issues everything that accumulates into Q
-    // (this product and [A_ak; A_rk] V) and commits it: an issuing thread stalls while the MMA queue is
-    // full, and a commit tracks the MMAs of its own thread only.
-    if (tid == kIssuerQ) {
-      tcgen05_fence_after_sync();
+      mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
       issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
     }
-    {
-      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
-      ++mma_uses;
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tcgen05_fence_after_sync();
-    }
+    bad |= !mbar_wait(bar_mma, mma_uses & 1);
+    ++mma_uses;
+    tcgen05_fence_after_sync();
 
     FRWKV_PHASE(2)
     // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
@@ -397,11 +391,11 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
-    __syncthreads();
+    if (__syncthreads_or(bad)) { failed = true; break; }
 
     FRWKV_PHASE(3)
     // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
-    if (tid == kIssuerQ) {
+    if (tid == 0) {
       tcgen05_fence_after_sync();
       issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
       mma_commit(bar_mma);
@@ -494,17 +488,14 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
       mma_commit(bar_mma);
     }
-    {
-      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
-      ++mma_uses;
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tcgen05_fence_after_sync();
-    }
+    bad |= !mbar_wait(bar_mma, mma_uses & 1);
+    ++mma_uses;
+    tcgen05_fence_after_sync();
     FRWKV_PHASE(6)
     rows_to_operand(kColU);
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
-    __syncthreads();
+    if (__syncthreads_or(bad)) { failed = true; break; }
 
     FRWKV_PHASE(7)
     // ================= Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V =================
@@ -516,12 +507,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
       mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMAs
     }
-    {
-      const bool ok = mbar_wait(bar_mma, mma_uses & 1);
-      ++mma_uses;
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tcgen05_fence_after_sync();
-    }
+    bad |= !mbar_wait(bar_mma, mma_uses & 1);
+    ++mma_uses;
+    tcgen05_fence_after_sync();
     FRWKV_PHASE(8)
     // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
     if (quad >= 2) {
@@ -545,11 +533,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         }
       }
     }
-    {
-      const bool ok = mbar_wait(bar_state, c & 1);
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tcgen05_fence_after_sync();
-    }
+    bad |= !mbar_wait(bar_state, c & 1);
+    tcgen05_fence_after_sync();
     // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
     {
       uint32_t regs[16];
@@ -578,7 +563,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
-    __syncthreads();
+    if (__syncthreads_or(bad)) { failed = true; break; }
     tcgen05_fence_after_sync();
     FRWKV_PHASE(9)
   }
