@@ -59,6 +59,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// ---- named barriers (bar.sync / bar.arrive): `threads` = every thread that arrives or waits, a multiple of 32 ----
+__device__ __forceinline__ void named_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_arrive(int id, int threads) {  // does not wait
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ bool named_sync_or(int id, int threads, bool pred) {  // barrier + OR of pred
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\tbar.red.or.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+
 // ---- proxies and fences ----------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -20,8 +20,12 @@ namespace {
 using namespace tc;
 using namespace chunk;
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
+constexpr int kWarps = 8;                       // compute warps
+constexpr int kComputeThreads = kWarps * 32;    // 256
+constexpr int kThreads = kComputeThreads + 32;  // + one warp that issues every MMA and TMA load
+// named barriers (0 is __syncthreads): the compute warps' own barrier, and four hand-offs on which the compute
+// threads arrive (without waiting) and the issuer warp waits
+constexpr int kBarCompute = 1, kBarOperands = 2, kBarMasks = 3, kBarInverse = 4, kBarU = 5;
 constexpr int kChunk = 32;
 
 // ---- shared-memory map (bytes) -------------------------------------------------------------
@@ -39,19 +43,18 @@ constexpr uint32_t kOffX3 = kOffX2 + 2 * kTileK64;    // [A_ak; A_rk] hi, lo (64
 constexpr uint32_t kOffX4 = kOffX3 + 2 * kTileK32;    // [T; A_rb] hi, lo (64 x 32)
 constexpr uint32_t kOffOp = kOffX4 + 2 * kTileK32;    // S0 (64 rows) / W / U (32 rows) operand hi, lo
 constexpr uint32_t kOffV = kOffOp + 2 * kTileK64;     // V operand hi, lo (32 rows x 64)
-constexpr uint32_t kOffMisc = kOffV + 2 * kTileV;     // gamma_L[64], group sums [8][64], barriers
-constexpr uint32_t kMiscBytes = 64 * 4 + kWarps * 64 * 4 + 64;
-constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 128;
-static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM's shared memory");
-// fp32 scratch of the 32x32 inverse, aliased onto the TMA staging area (free after stage A; the next
-// chunk's load is issued once the inverse is done).  [At; Rt] cannot host it: Q = [At; Rt] S0 is still
-// being computed while P is read back.
+constexpr uint32_t kOffMisc = kOffV + 2 * kTileV;     // gamma_L[2][64], group sums [8][64], barriers
+constexpr uint32_t kMiscBytes = 2 * 64 * 4 + kWarps * 64 * 4 + 64;
+// fp32 scratch of the 32x32 inverse.  It has its own area: the staging area must stay free for the next chunk's
+// load, which is issued a whole chunk ahead.  The 16x16 block product of level 1 lives in T's upper-right block,
+// which is zero and never stored.
 constexpr int kInvLd = 36;
-constexpr uint32_t kOffAb = kOffRaw;                   // A_ab [32][36]
+constexpr uint32_t kOffAb = kOffMisc + kMiscBytes;     // A_ab [32][36]
 constexpr uint32_t kOffTi = kOffAb + 32 * kInvLd * 4;  // T    [32][36]
-constexpr int kMbLd = 17;
-constexpr uint32_t kOffMb = kOffTi + 32 * kInvLd * 4;  // block product [16][17]
-static_assert(kOffMb + 16 * kMbLd * 4 <= kOffX1, "inverse scratch must fit in the staging area");
+constexpr int kMbLd = kInvLd;
+constexpr uint32_t kOffMb = kOffTi + 16 * 4;           // block product [16][16] at T[0..15][16..31]
+constexpr uint32_t kSmemBytes = kOffTi + 32 * kInvLd * 4 + 128;
+static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM's shared memory");
 
 // ---- TMEM map (columns) --------------------------------------------------------------------
 constexpr uint32_t kTmemCols = 256;
@@ -84,11 +87,12 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   const int slot = p.slots[seq];
 
   float* gamma_l = reinterpret_cast<float*>(smem + kOffMisc);
-  float* group_sum = gamma_l + 64;  // [8][64] log2-decay sums of each 4-row group
+  float* group_sum = gamma_l + 2 * 64;  // [8][64] log2-decay sums of each 4-row group (gamma_l: [2][64] by chunk parity)
   uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_sum + kWarps * 64);
   uint64_t* bar_mma = bar_tma + 1;
   uint64_t* bar_state = bar_tma + 2;  // its own barrier: two commits may not complete two phases of one
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_state + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;  // set by the compute warps when a bounded wait gave up
   const uint32_t sbase = smem_u32(smem);
 
   if (tid == 0) {
@@ -96,6 +100,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     mbar_init(bar_mma, 1);
     mbar_init(bar_state, 1);
     mbar_fence_init();
+    *abort_flag = 0u;
     tma_prefetch_descriptor(&maps.r);
     tma_prefetch_descriptor(&maps.w);
     tma_prefetch_descriptor(&maps.k);
@@ -163,7 +168,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
   // ---- initial state: global -> TMEM (fp32) and -> S0 operand tile ----------------------------
   float* state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
-  {
+  const bool compute_warp = warp < kWarps;
+  if (compute_warp) {
     uint32_t regs[32];
     if (row_lane) {
       const float4* src = reinterpret_cast<const float4*>(state_g + arow * kHeadDim + half * 32);
@@ -214,7 +220,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
   };
 
-  uint32_t mma_uses = 0;
   bool failed = false;
   bool bad = false;  // this thread saw a bounded wait give up; turned into `failed` at the next CTA barrier
 #ifdef FRWKV_CHUNK_TIMING
@@ -222,350 +227,407 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 #endif
   const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
 
-  for (int c = 0; c < n_chunks; ++c) {
-    const int rows = min(kChunk, len - c * kChunk);
-    const int row0 = t_begin + c * kChunk;
+  // ---- operand preparation of one chunk (decay products, scaled operands) -----------------------------------
+  // It depends on the tokens only, so it runs for chunk c+1 while the tensor pipe works on chunk c's last
+  // products.  [At; Rt] goes straight to its tile (free since Q was read); [Bt; Kt] and V, whose tiles the state
+  // MMAs of chunk c still read, stay in these registers until release_operands().
+  uint32_t held_x2[16];  // per row of this thread: Bt hi, Bt lo, Kt hi, Kt lo
+  uint4 held_v_hi, held_v_lo = make_uint4(0u, 0u, 0u, 0u);
+  auto prepare_operands = [&](int chunk, float* gamma_dst) -> bool {  // all threads; one CTA barrier inside
+    const int rows = min(kChunk, len - chunk * kChunk);
+    const bool ok = mbar_wait(bar_tma, tma_parity);
+    tma_in_flight = false;
+    tma_parity ^= 1u;
+    constexpr int kRowsPerWarp = kChunk / kWarps;  // 4
+    const int kp = lane;                           // key channels 2*kp, 2*kp+1
+    const int tg = warp;                           // rows 4*tg .. 4*tg+3
+    const uint32_t* raw_r = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 0 * kRawTile);
+    const uint32_t* raw_w = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 1 * kRawTile);
+    const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
+    const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
+    const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
+    float2 bias2 = make_float2(0.f, 0.f);
+    if (bias_g != nullptr) bias2 = make_float2(to_f32(bias_g[2 * kp]), to_f32(bias_g[2 * kp + 1]));
+    float2 run = make_float2(0.f, 0.f);
+    float2 cum[kRowsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) {
+      const int t = tg * kRowsPerWarp + i;
+      const float2 w2 = unpack2<io_t>(raw_w[t * 32 + kp]);
+      float2 l;
+      if constexpr (LOGITS) {
+        l.x = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.x + bias2.x)));
+        l.y = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.y + bias2.y)));
+      } else {
+        l.x = fast_log2(w2.x);
+        l.y = fast_log2(w2.y);
+      }
+      if (t >= rows) l = make_float2(0.f, 0.f);
+      run.x += l.x;
+      run.y += l.y;
+      cum[i] = run;
+    }
+    reinterpret_cast<float2*>(group_sum + tg * 64)[kp] = run;
+    // V operand: rows = token, 64 contiguous value columns (MN-major); bf16 is copied, fp16 is split
+    {
+      const uint8_t* raw_v = smem + kOffRaw + 3 * kRawTile;
+      const int sr = tid >> 3, vc = tid & 7;  // 256 chunks of 8 values
+      uint4 q = *reinterpret_cast<const uint4*>(raw_v + sr * 128 + vc * 16);
+      if (sr >= rows) q = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (kVExact) {
+        held_v_hi = q;
+      } else {
+        float x[8];
+        const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack2<io_t>(words[e]);
+          x[2 * e] = f.x;
+          x[2 * e + 1] = f.y;
+        }
+        split8(x, held_v_hi, held_v_lo);
+      }
+    }
+    named_sync(kBarCompute, kComputeThreads);
+    float2 off = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int g = 0; g < kWarps - 1; ++g) {  // loads issued together; only the adds are a chain
+      const float2 sgrp = reinterpret_cast<const float2*>(group_sum + g * 64)[kp];
+      if (g < tg) {
+        off.x += sgrp.x;
+        off.y += sgrp.y;
+      }
+    }
+    float2 g_prev = make_float2(fast_exp2(off.x), fast_exp2(off.y));
+    uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kStride64 + (kp & 3) * 4;
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) {
+      const int t = tg * kRowsPerWarp + i;
+      const bool live = t < rows;
+      const float2 lg = make_float2(off.x + cum[i].x, off.y + cum[i].y);
+      const float2 g = make_float2(fast_exp2(lg.x), fast_exp2(lg.y));
+      const float2 gi = make_float2(fast_exp2(-lg.x), fast_exp2(-lg.y));
+      const float2 gx = g_prev;  // exclusive product = inclusive product of the previous row
+      g_prev = g;
+      float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
+      float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
+      float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
+      float2 b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
+      if (!live) {
+        r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
+      }
+      const uint32_t row_lo = (t >> 3) * kRowGroup + (t & 7) * 16;         // rows 0..31
+      const uint32_t row_hi = ((t + 32) >> 3) * kRowGroup + (t & 7) * 16;  // rows 32..63
+      uint32_t h, l;
+      split2(a2.x * gx.x, a2.y * gx.y, h, l);
+      *reinterpret_cast<uint32_t*>(x1 + row_lo) = h;
+      *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_lo) = l;
+      split2(r2.x * g.x, r2.y * g.y, h, l);
+      *reinterpret_cast<uint32_t*>(x1 + row_hi) = h;
+      *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_hi) = l;
+      split2(b2.x * gi.x, b2.y * gi.y, held_x2[4 * i], held_x2[4 * i + 1]);
+      split2(k2.x * gi.x, k2.y * gi.y, held_x2[4 * i + 2], held_x2[4 * i + 3]);
+      if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_dst)[kp] = g;
+    }
+    return ok;
+  };
+  auto release_operands = [&]() {  // [Bt; Kt] and V of the prepared chunk: registers -> tiles
+    const int kp = lane, tg = warp;
+    uint8_t* x2 = smem + kOffX2 + (kp >> 2) * kStride64 + (kp & 3) * 4;
+#pragma unroll
+    for (int i = 0; i < kChunk / kWarps; ++i) {
+      const int t = tg * (kChunk / kWarps) + i;
+      const uint32_t row_lo = (t >> 3) * kRowGroup + (t & 7) * 16;
+      const uint32_t row_hi = ((t + 32) >> 3) * kRowGroup + (t & 7) * 16;
+      *reinterpret_cast<uint32_t*>(x2 + row_lo) = held_x2[4 * i];
+      *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_lo) = held_x2[4 * i + 1];
+      *reinterpret_cast<uint32_t*>(x2 + row_hi) = held_x2[4 * i + 2];
+      *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_hi) = held_x2[4 * i + 3];
+    }
+    const int sr = tid >> 3, vc = tid & 7;
+    uint8_t* dst = smem + kOffV + vc * kStride32 + (sr & 7) * 16 + (sr >> 3) * kRowGroup;
+    *reinterpret_cast<uint4*>(dst) = held_v_hi;
+    if constexpr (!kVExact) *reinterpret_cast<uint4*>(dst + kTileV) = held_v_lo;
+  };
 
-    // ================= stage A: decay products and scaled operands =================
-    {
-      const bool ok = mbar_wait(bar_tma, tma_parity);
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tma_in_flight = false;
-      tma_parity ^= 1u;
-    }
-    FRWKV_PHASE(0)
-    {
-      constexpr int kRowsPerWarp = kChunk / kWarps;  // 4
-      const int kp = lane;                           // key channels 2*kp, 2*kp+1
-      const int tg = warp;                           // rows 4*tg .. 4*tg+3
-      const uint32_t* raw_r = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 0 * kRawTile);
-      const uint32_t* raw_w = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 1 * kRawTile);
-      const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
-      const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
-      const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
-      float2 bias2 = make_float2(0.f, 0.f);
-      if (bias_g != nullptr) bias2 = make_float2(to_f32(bias_g[2 * kp]), to_f32(bias_g[2 * kp + 1]));
-      float2 run = make_float2(0.f, 0.f);
-      float2 cum[kRowsPerWarp];
-#pragma unroll
-      for (int i = 0; i < kRowsPerWarp; ++i) {
-        const int t = tg * kRowsPerWarp + i;
-        const float2 w2 = unpack2<io_t>(raw_w[t * 32 + kp]);
-        float2 l;
-        if constexpr (LOGITS) {
-          l.x = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.x + bias2.x)));
-          l.y = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.y + bias2.y)));
-        } else {
-          l.x = fast_log2(w2.x);
-          l.y = fast_log2(w2.y);
-        }
-        if (t >= rows) l = make_float2(0.f, 0.f);
-        run.x += l.x;
-        run.y += l.y;
-        cum[i] = run;
-      }
-      reinterpret_cast<float2*>(group_sum + tg * 64)[kp] = run;
-      // V operand: rows = token, 64 contiguous value columns (MN-major); bf16 is copied, fp16 is split
-      {
-        const uint8_t* raw_v = smem + kOffRaw + 3 * kRawTile;
-        const int s = tid >> 3, vc = tid & 7;  // 256 chunks of 8 values
-        uint4 q = *reinterpret_cast<const uint4*>(raw_v + s * 128 + vc * 16);
-        uint8_t* dst = smem + kOffV + vc * kStride32 + (s & 7) * 16 + (s >> 3) * kRowGroup;
-        if (s >= rows) q = make_uint4(0u, 0u, 0u, 0u);
-        if constexpr (kVExact) {
-          *reinterpret_cast<uint4*>(dst) = q;
-        } else {
-          float x[8];
-          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = unpack2<io_t>(words[e]);
-            x[2 * e] = f.x;
-            x[2 * e + 1] = f.y;
-          }
-          uint4 hi, lo;
-          split8(x, hi, lo);
-          *reinterpret_cast<uint4*>(dst) = hi;
-          *reinterpret_cast<uint4*>(dst + kTileV) = lo;
-        }
-      }
-      __syncthreads();
-      FRWKV_PHASE(12)
-      float2 off = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int g = 0; g < kWarps - 1; ++g) {  // loads issued together; only the adds are a chain
-        const float2 sgrp = reinterpret_cast<const float2*>(group_sum + g * 64)[kp];
-        if (g < tg) {
-          off.x += sgrp.x;
-          off.y += sgrp.y;
-        }
-      }
-      float2 g_prev = make_float2(fast_exp2(off.x), fast_exp2(off.y));
-      uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kStride64 + (kp & 3) * 4;
-      uint8_t* x2 = smem + kOffX2 + (kp >> 2) * kStride64 + (kp & 3) * 4;
-#pragma unroll
-      for (int i = 0; i < kRowsPerWarp; ++i) {
-        const int t = tg * kRowsPerWarp + i;
-        const bool live = t < rows;
-        const float2 lg = make_float2(off.x + cum[i].x, off.y + cum[i].y);
-        const float2 g = make_float2(fast_exp2(lg.x), fast_exp2(lg.y));
-        const float2 gi = make_float2(fast_exp2(-lg.x), fast_exp2(-lg.y));
-        const float2 gx = g_prev;  // exclusive product = inclusive product of the previous row
-        g_prev = g;
-        float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
-        float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
-        float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
-        float2 b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
-        if (!live) {
-          r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
-        }
-        const uint32_t row_lo = (t >> 3) * kRowGroup + (t & 7) * 16;         // rows 0..31
-        const uint32_t row_hi = ((t + 32) >> 3) * kRowGroup + (t & 7) * 16;  // rows 32..63
-        uint32_t h, l;
-        split2(a2.x * gx.x, a2.y * gx.y, h, l);
-        *reinterpret_cast<uint32_t*>(x1 + row_lo) = h;
-        *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_lo) = l;
-        split2(r2.x * g.x, r2.y * g.y, h, l);
-        *reinterpret_cast<uint32_t*>(x1 + row_hi) = h;
-        *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_hi) = l;
-        split2(b2.x * gi.x, b2.y * gi.y, h, l);
-        *reinterpret_cast<uint32_t*>(x2 + row_lo) = h;
-        *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_lo) = l;
-        split2(k2.x * gi.x, k2.y * gi.y, h, l);
-        *reinterpret_cast<uint32_t*>(x2 + row_hi) = h;
-        *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_hi) = l;
-        if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_l)[kp] = g;
-      }
-    }
+  uint32_t mma_phase = 0;  // completed phases of bar_mma, counted the same way by every compute thread
+
+  if (compute_warp) {
+    // =====================================================================================================
+    // Compute warps.  They never wait for the issuer warp except through the MMA mbarriers (bounded waits);
+    // at each hand-off they arrive on a named barrier and go on.  Once a wait has given up (`failed`, agreed on
+    // at a compute barrier) they skip all work but still make every arrival of the chunk, so that the issuer
+    // warp, which reads `abort_flag` after the first hand-off of each chunk, always gets out of its barriers.
+    // =====================================================================================================
+    // chunk 0 is prepared up front; afterwards every chunk prepares its successor
+    bad |= !prepare_operands(0, gamma_l);
+    release_operands();
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
-    __syncthreads();
+    failed = named_sync_or(kBarCompute, kComputeThreads, bad);
+    if (failed && tid == 0) *abort_flag = 1u;
 
-    FRWKV_PHASE(1)
-    // ================= P = X1 X2^T ; Q = X1 S0 =================
-    // One thread issues every MMA, in the order the results are needed: the tensor pipe runs them first in,
-    // first out.  The issuer stalls while the MMA queue is full, so no CTA-wide barrier follows an MMA wait: each
-    // warp goes on as soon as the mbarrier flips, and a wait that gave up is reported at the next barrier.
-    if (tid == 0) {
+    for (int c = 0; c < n_chunks; ++c) {
+      const int rows = min(kChunk, len - c * kChunk);
+      const int row0 = t_begin + c * kChunk;
+      // ---- hand-off: [At; Rt], [Bt; Kt], V and S0 of chunk c are in place; the staging area is free ----
+      named_arrive(kBarOperands, kThreads);
+      if (failed) break;
+      if (c + 1 < n_chunks) tma_in_flight = true;  // the issuer warp loads the next chunk's tokens now
+      FRWKV_PHASE(0)
+
+      // ================= P = X1 X2^T (the issuer warp also starts Q = X1 S0, which runs under the read-back) ====
+      bad |= !mbar_wait(bar_mma, mma_phase & 1);
+      ++mma_phase;
       tcgen05_fence_after_sync();
-      issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
-      mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
-      issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
-    }
-    bad |= !mbar_wait(bar_mma, mma_uses & 1);
-    ++mma_uses;
-    tcgen05_fence_after_sync();
-
-    FRWKV_PHASE(2)
-    // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
-    {
-      // accumulator row arow: rows 0..31 belong to At (quadrants 0,1), rows 32..63 to Rt (quadrants 2,3);
-      // columns 32*half..: half 0 = products with Bt (A_ab / A_rb), half 1 = with Kt (A_ak / A_rk)
-      uint32_t regs[16];
-      tmem_ld_frag16(tmem_lane + kColP + half * 32, regs);
-      tmem_ld_wait();
-      float vals[16];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int t = (frow0 + 8 * h) & 31;
-        const int limit = quad < 2 ? t : t + 1;  // keep columns s < limit
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e)
-            vals[4 * n + 2 * h + e] = 8 * n + 2 * fq + e < limit ? __uint_as_float(regs[4 * n + 2 * h + e]) : 0.0f;
-        }
-      }
-      if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
+      FRWKV_PHASE(2)
+      // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
+      {
+        // accumulator row arow: rows 0..31 belong to At (quadrants 0,1), rows 32..63 to Rt (quadrants 2,3);
+        // columns 32*half..: half 0 = products with Bt (A_ab / A_rb), half 1 = with Kt (A_ak / A_rk)
+        uint32_t regs[16];
+        tmem_ld_frag16(tmem_lane + kColP + half * 32, regs);
+        tmem_ld_wait();
+        float vals[16];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          float* dst = reinterpret_cast<float*>(smem + kOffAb) + (frow0 + 8 * h) * kInvLd + 2 * fq;
-#pragma unroll
-          for (int n = 0; n < 4; ++n)
-            *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(vals[4 * n + 2 * h], vals[4 * n + 2 * h + 1]);
-        }
-      } else {
-        // half 1: A_ak -> X3 rows 0..31 (quad<2), A_rk -> X3 rows 32..63; half 0, quad>=2: A_rb -> X4 rows 32..63
-        store_operand_frag(half == 1 ? kOffX3 : kOffX4, kTileK32, 0, vals);
-      }
-    }
-    fence_proxy_async_smem();
-    tcgen05_fence_before_sync();
-    if (__syncthreads_or(bad)) { failed = true; break; }
-
-    FRWKV_PHASE(3)
-    // ================= Q += [A_ak; A_rk] V (async) while the inverse runs on CUDA cores =================
-    if (tid == 0) {
-      tcgen05_fence_after_sync();
-      issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
-      mma_commit(bar_mma);
-    }
-    {
-      float* ab = reinterpret_cast<float*>(smem + kOffAb);
-      float* ti = reinterpret_cast<float*>(smem + kOffTi);
-      float* mb = reinterpret_cast<float*>(smem + kOffMb);
-      bool w_ready = true;
-      // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread, on a warp
-      // that has no accumulator rows to read back; meanwhile the warps of quadrants 0,1 wait for Q and
-      // turn W = Q rows 0..31 into the operand tile, and the remaining warps clear T's upper block
-      if (warp == 2) {
-        const int d = lane >> 4, j = lane & 15;
-        const float* blk = ab + (16 * d) * kInvLd + 16 * d;
-        float part[16];  // right-looking substitution: part[t] collects the row sums as columns finish
-#pragma unroll
-        for (int t = 0; t < 16; ++t) part[t] = t == j ? 1.0f : 0.0f;
-#pragma unroll
-        for (int s2 = 0; s2 < 16; ++s2) {
-          const float xs = part[s2];  // x[s2] is final: every earlier column has been folded in
-          ti[(16 * d + s2) * kInvLd + 16 * d + j] = xs;
-#pragma unroll
-          for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
-        }
-      } else if (quad >= 2) {  // warps 3, 6, 7: zero the block above the diagonal (rows 0..15, columns 16..31)
-        const int e0 = (warp == 3 ? 0 : warp == 6 ? 1 : 2) * 32 + lane;
-        for (int e = e0; e < 256; e += 96) ti[(e >> 4) * kInvLd + 16 + (e & 15)] = 0.0f;
-      } else {
-        w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_uses & 1));
-        tcgen05_fence_after_sync();
-        if (w_ready) rows_to_operand(kColQ);
-      }
-      ++mma_uses;
-      if (__syncthreads_or(!w_ready)) { failed = true; break; }
-      FRWKV_PHASE(10)
-      // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
-      {
-        const int rr = tid >> 4, cc = tid & 15;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four independent partial sums: no 16-deep FMA chain
-#pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) {
-          const float4 av = *reinterpret_cast<const float4*>(ab + (16 + rr) * kInvLd + 4 * s4);
-          acc[0] = fmaf(av.x, ti[(4 * s4 + 0) * kInvLd + cc], acc[0]);
-          acc[1] = fmaf(av.y, ti[(4 * s4 + 1) * kInvLd + cc], acc[1]);
-          acc[2] = fmaf(av.z, ti[(4 * s4 + 2) * kInvLd + cc], acc[2]);
-          acc[3] = fmaf(av.w, ti[(4 * s4 + 3) * kInvLd + cc], acc[3]);
-        }
-        mb[rr * kMbLd + cc] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-        __syncthreads();
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
-#pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) {
-          const float4 dv = *reinterpret_cast<const float4*>(ti + (16 + rr) * kInvLd + 16 + 4 * s4);
-          acc[0] = fmaf(dv.x, mb[(4 * s4 + 0) * kMbLd + cc], acc[0]);
-          acc[1] = fmaf(dv.y, mb[(4 * s4 + 1) * kMbLd + cc], acc[1]);
-          acc[2] = fmaf(dv.z, mb[(4 * s4 + 2) * kMbLd + cc], acc[2]);
-          acc[3] = fmaf(dv.w, mb[(4 * s4 + 3) * kMbLd + cc], acc[3]);
-        }
-        ti[(16 + rr) * kInvLd + cc] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      }
-      __syncthreads();
-      FRWKV_PHASE(11)
-      // T -> rows 0..31 of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
-      if (tid < 128) {
-        const int t = tid >> 2, cj = tid & 3;
-        const float4 f0 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8);
-        const float4 f1 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8 + 4);
-        const float x[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-        uint4 hi, lo;
-        split8(x, hi, lo);
-        uint8_t* dst = smem + kOffX4 + (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64;
-        *reinterpret_cast<uint4*>(dst) = hi;
-        *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
-      }
-    }
-    FRWKV_PHASE(4)
-    fence_proxy_async_smem();
-    tcgen05_fence_before_sync();
-    __syncthreads();
-
-    FRWKV_PHASE(5)
-    // ================= U = T W  (rows 32..63 of this product are unused) =================
-    // the staging area (and the inverse scratch in it) is free: start the next chunk's load, from a thread
-    // other than the MMA issuer
-    if (tid == 32 && c + 1 < n_chunks) issue_tma(c + 1);
-    if (c + 1 < n_chunks) tma_in_flight = true;
-    if (tid == 0) {
-      tcgen05_fence_after_sync();
-      issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
-      mma_commit(bar_mma);
-    }
-    bad |= !mbar_wait(bar_mma, mma_uses & 1);
-    ++mma_uses;
-    tcgen05_fence_after_sync();
-    FRWKV_PHASE(6)
-    rows_to_operand(kColU);
-    fence_proxy_async_smem();
-    tcgen05_fence_before_sync();
-    if (__syncthreads_or(bad)) { failed = true; break; }
-
-    FRWKV_PHASE(7)
-    // ================= Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V =================
-    if (tid == 0) {
-      tcgen05_fence_after_sync();
-      issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
-      mma_commit(bar_mma);  // Y is complete when this one arrives ...
-      issue_gemm<true, true, 2>(tmem + kColS, op_bt, op_rows, idesc_mnmn, true);
-      issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
-      mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMAs
-    }
-    bad |= !mbar_wait(bar_mma, mma_uses & 1);
-    ++mma_uses;
-    tcgen05_fence_after_sync();
-    FRWKV_PHASE(8)
-    // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
-    if (quad >= 2) {
-      uint32_t regs[16];
-      tmem_ld_frag16(tmem_lane + kColQ + half * 32, regs);
-      tmem_ld_wait();
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int t = frow0 + 8 * h - 32;
-        if (t < rows) {
-          const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
-          io_t* yp = static_cast<io_t*>(p.y) + out;
+          const int t = (frow0 + 8 * h) & 31;
+          const int limit = quad < 2 ? t : t + 1;  // keep columns s < limit
 #pragma unroll
           for (int n = 0; n < 4; ++n) {
-            const float y0 = __uint_as_float(regs[4 * n + 2 * h]) * p.scale;
-            const float y1 = __uint_as_float(regs[4 * n + 2 * h + 1]) * p.scale;
-            alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
-            *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
-            if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+              vals[4 * n + 2 * h + e] = 8 * n + 2 * fq + e < limit ? __uint_as_float(regs[4 * n + 2 * h + e]) : 0.0f;
           }
         }
-      }
-    }
-    bad |= !mbar_wait(bar_state, c & 1);
-    tcgen05_fence_after_sync();
-    // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
-    {
-      uint32_t regs[16];
-      tmem_ld_frag16(tmem_lane + kColS + half * 32, regs);
-      tmem_ld_wait();
-      const float gl[2] = {gamma_l[frow0], gamma_l[frow0 + 8]};
-      float x[16];
+        if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        x[i] = __uint_as_float(regs[i]) * gl[(i >> 1) & 1];
-        regs[i] = __float_as_uint(x[i]);
-      }
-      if (c + 1 < n_chunks) {
-        tmem_st_frag16(tmem_lane + kColS + half * 32, regs);
-        store_operand_frag(kOffOp, kTileK64, half * 4, x);
-        tmem_st_wait();
-      } else {
+          for (int h = 0; h < 2; ++h) {
+            float* dst = reinterpret_cast<float*>(smem + kOffAb) + (frow0 + 8 * h) * kInvLd + 2 * fq;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float* dst = state_g + (frow0 + 8 * h) * kHeadDim + half * 32 + 2 * fq;
-#pragma unroll
-          for (int n = 0; n < 4; ++n)
-            __stcs(reinterpret_cast<float2*>(dst + 8 * n), make_float2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1]));
+            for (int n = 0; n < 4; ++n)
+              *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(vals[4 * n + 2 * h], vals[4 * n + 2 * h + 1]);
+          }
+        } else {
+          // half 1: A_ak -> X3 rows 0..31 (quad<2), A_rk -> X3 rows 32..63; half 0, quad>=2: A_rb -> X4 rows 32..63
+          store_operand_frag(half == 1 ? kOffX3 : kOffX4, kTileK32, 0, vals);
         }
       }
+      fence_proxy_async_smem();
+      tcgen05_fence_before_sync();
+      named_arrive(kBarMasks, kThreads);  // -> Q += [A_ak; A_rk] V
+      failed = named_sync_or(kBarCompute, kComputeThreads, bad);  // A_ab scratch visible to the inverse
+      FRWKV_PHASE(3)
+
+      // ================= 32x32 inverse on CUDA cores while Q is finished by the tensor pipe =================
+      if (!failed) {
+        float* ab = reinterpret_cast<float*>(smem + kOffAb);
+        float* ti = reinterpret_cast<float*>(smem + kOffTi);
+        float* mb = reinterpret_cast<float*>(smem + kOffMb);
+        bool w_ready = true;
+        // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread, on a warp
+        // that has no accumulator rows to read back; meanwhile the warps of quadrants 0,1 wait for Q and
+        // turn W = Q rows 0..31 into the operand tile, and the remaining warps clear T's upper block
+        if (warp == 2) {
+          const int d = lane >> 4, j = lane & 15;
+          const float* blk = ab + (16 * d) * kInvLd + 16 * d;
+          float part[16];  // right-looking substitution: part[t] collects the row sums as columns finish
+#pragma unroll
+          for (int t = 0; t < 16; ++t) part[t] = t == j ? 1.0f : 0.0f;
+#pragma unroll
+          for (int s2 = 0; s2 < 16; ++s2) {
+            const float xs = part[s2];  // x[s2] is final: every earlier column has been folded in
+            ti[(16 * d + s2) * kInvLd + 16 * d + j] = xs;
+#pragma unroll
+            for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
+          }
+        } else if (quad >= 2) {  // warps 3, 6, 7: nothing to do until level 1
+        } else {
+          w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_phase & 1));
+          tcgen05_fence_after_sync();
+          if (w_ready) rows_to_operand(kColQ);
+        }
+        ++mma_phase;
+        bad |= !w_ready;
+        named_sync(kBarCompute, kComputeThreads);
+        FRWKV_PHASE(10)
+        // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
+        {
+          const int rr = tid >> 4, cc = tid & 15;
+          float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four independent partial sums: no 16-deep FMA chain
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const float4 av = *reinterpret_cast<const float4*>(ab + (16 + rr) * kInvLd + 4 * s4);
+            acc[0] = fmaf(av.x, ti[(4 * s4 + 0) * kInvLd + cc], acc[0]);
+            acc[1] = fmaf(av.y, ti[(4 * s4 + 1) * kInvLd + cc], acc[1]);
+            acc[2] = fmaf(av.z, ti[(4 * s4 + 2) * kInvLd + cc], acc[2]);
+            acc[3] = fmaf(av.w, ti[(4 * s4 + 3) * kInvLd + cc], acc[3]);
+          }
+          mb[rr * kMbLd + cc] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+          named_sync(kBarCompute, kComputeThreads);
+          acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const float4 dv = *reinterpret_cast<const float4*>(ti + (16 + rr) * kInvLd + 16 + 4 * s4);
+            acc[0] = fmaf(dv.x, mb[(4 * s4 + 0) * kMbLd + cc], acc[0]);
+            acc[1] = fmaf(dv.y, mb[(4 * s4 + 1) * kMbLd + cc], acc[1]);
+            acc[2] = fmaf(dv.z, mb[(4 * s4 + 2) * kMbLd + cc], acc[2]);
+            acc[3] = fmaf(dv.w, mb[(4 * s4 + 3) * kMbLd + cc], acc[3]);
+          }
+          ti[(16 + rr) * kInvLd + cc] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
+        named_sync(kBarCompute, kComputeThreads);
+        FRWKV_PHASE(11)
+        // T -> rows 0..31 of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
+        if (tid < 128) {
+          const int t = tid >> 2, cj = tid & 3;
+          float4 f0 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8);
+          float4 f1 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8 + 4);
+          if (t < 16 && cj >= 2) f0 = f1 = make_float4(0.f, 0.f, 0.f, 0.f);  // block above the diagonal (holds scratch)
+          const float x[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+          uint4 hi, lo;
+          split8(x, hi, lo);
+          uint8_t* dst = smem + kOffX4 + (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64;
+          *reinterpret_cast<uint4*>(dst) = hi;
+          *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
+        }
+      }
+      else {
+        ++mma_phase;
+        named_sync(kBarCompute, kComputeThreads);
+        named_sync(kBarCompute, kComputeThreads);
+        named_sync(kBarCompute, kComputeThreads);
+      }
+      FRWKV_PHASE(4)
+      fence_proxy_async_smem();
+      tcgen05_fence_before_sync();
+      named_arrive(kBarInverse, kThreads);  // -> U = T W (rows 32..63 of this product are unused)
+      FRWKV_PHASE(5)
+
+      if (!failed) {
+        bad |= !mbar_wait(bar_mma, mma_phase & 1);
+        tcgen05_fence_after_sync();
+        FRWKV_PHASE(6)
+        rows_to_operand(kColU);
+      }
+      ++mma_phase;
+      fence_proxy_async_smem();
+      tcgen05_fence_before_sync();
+      named_arrive(kBarU, kThreads);  // -> Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V
+      FRWKV_PHASE(7)
+
+      // the tensor pipe is busy with Y and S: prepare the next chunk's operands meanwhile
+      if (!failed && c + 1 < n_chunks) bad |= !prepare_operands(c + 1, gamma_l + ((c + 1) & 1) * 64);
+      FRWKV_PHASE(1)
+      if (!failed) {
+        bad |= !mbar_wait(bar_mma, mma_phase & 1);
+        tcgen05_fence_after_sync();
+        FRWKV_PHASE(8)
+        // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
+        if (quad >= 2) {
+          uint32_t regs[16];
+          tmem_ld_frag16(tmem_lane + kColQ + half * 32, regs);
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int t = frow0 + 8 * h - 32;
+            if (t < rows) {
+              const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
+              io_t* yp = static_cast<io_t*>(p.y) + out;
+#pragma unroll
+              for (int n = 0; n < 4; ++n) {
+                const float y0 = __uint_as_float(regs[4 * n + 2 * h]) * p.scale;
+                const float y1 = __uint_as_float(regs[4 * n + 2 * h + 1]) * p.scale;
+                alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
+                *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
+                if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
+              }
+            }
+          }
+        }
+        bad |= !mbar_wait(bar_state, c & 1);
+        tcgen05_fence_after_sync();
+        // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
+        {
+          uint32_t regs[16];
+          tmem_ld_frag16(tmem_lane + kColS + half * 32, regs);
+          tmem_ld_wait();
+          const float* gamma_c = gamma_l + (c & 1) * 64;
+          const float gl[2] = {gamma_c[frow0], gamma_c[frow0 + 8]};
+          float x[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            x[i] = __uint_as_float(regs[i]) * gl[(i >> 1) & 1];
+            regs[i] = __float_as_uint(x[i]);
+          }
+          if (c + 1 < n_chunks) {
+            tmem_st_frag16(tmem_lane + kColS + half * 32, regs);
+            store_operand_frag(kOffOp, kTileK64, half * 4, x);
+            tmem_st_wait();
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              float* dst = state_g + (frow0 + 8 * h) * kHeadDim + half * 32 + 2 * fq;
+#pragma unroll
+              for (int n = 0; n < 4; ++n)
+                __stcs(reinterpret_cast<float2*>(dst + 8 * n), make_float2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1]));
+            }
+          }
+        }
+        // this thread has seen the state MMAs finish: their [Bt; Kt] and V tiles may take the next chunk's values
+        if (c + 1 < n_chunks) release_operands();
+      }
+      ++mma_phase;
+      fence_proxy_async_smem();
+      tcgen05_fence_before_sync();
+      failed |= named_sync_or(kBarCompute, kComputeThreads, bad);
+      if (failed && tid == 0) *abort_flag = 1u;  // before the next arrival on kBarOperands
+      tcgen05_fence_after_sync();
+      FRWKV_PHASE(9)
     }
-    fence_proxy_async_smem();
-    tcgen05_fence_before_sync();
-    if (__syncthreads_or(bad)) { failed = true; break; }
-    tcgen05_fence_after_sync();
-    FRWKV_PHASE(9)
+  } else {
+    // =====================================================================================================
+    // Issuer warp: lane 0 issues every TMA load and every MMA, in the order the results are needed (the tensor
+    // pipe runs them first in, first out).  An issuing thread stalls while the MMA queue is full, at about the
+    // rate the MMAs execute, so none of the compute warps issues anything.  The warp waits on named barriers
+    // only; the compute warps make every arrival of a chunk even after a failure.
+    // =====================================================================================================
+    for (int c = 0; c < n_chunks; ++c) {
+      named_sync(kBarOperands, kThreads);
+      if (*abort_flag != 0u) break;
+      if (lane == 0) {
+        tcgen05_fence_after_sync();
+        if (c + 1 < n_chunks) issue_tma(c + 1);  // a whole chunk ahead of its use
+        issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
+        mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
+        issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
+      }
+      __syncwarp();
+      named_sync(kBarMasks, kThreads);
+      if (lane == 0) {
+        tcgen05_fence_after_sync();
+        issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
+        mma_commit(bar_mma);  // Q complete (commits track every earlier MMA of the thread)
+      }
+      __syncwarp();
+      named_sync(kBarInverse, kThreads);
+      if (lane == 0) {
+        tcgen05_fence_after_sync();
+        issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
+        mma_commit(bar_mma);
+      }
+      __syncwarp();
+      named_sync(kBarU, kThreads);
+      if (lane == 0) {
+        tcgen05_fence_after_sync();
+        issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
+        mma_commit(bar_mma);  // Y is complete when this one arrives ...
+        issue_gemm<true, true, 2>(tmem + kColS, op_bt, op_rows, idesc_mnmn, true);
+        issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
+        mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMAs
+      }
+      __syncwarp();
+    }
   }
 
   if (failed) {

@@ -19,7 +19,7 @@ constexpr uint32_t kRowGroup = 128;  // one core-matrix row group: 8 rows x 16 B
 #ifdef FRWKV_CHUNK_TIMING
 __device__ long long g_phase_ticks[16];
 #define FRWKV_PHASE(i)                                        \
-  if (tid == 0 && blockIdx.x == 0) {                          \
+  if (tid == 255 && blockIdx.x == 0) {                        \
     const long long now = clock64();                          \
     g_phase_ticks[i] += now - phase_t0;                       \
     phase_t0 = now;                                           \
