@@ -597,10 +597,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
-        if (c + 1 < n_chunks) issue_tma(c + 1);  // a whole chunk ahead of its use
         issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
         mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
         issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
+        if (c + 1 < n_chunks) issue_tma(c + 1);  // a whole chunk ahead of its use; after the MMAs, which are waited for
       }
       __syncwarp();
       named_sync(kBarMasks, kThreads);
