@@ -3,10 +3,12 @@
 // Same algebra, precision scheme and data movement as the 64-row kernel in chunk_tc.cu (see the
 // header there); what changes is the footprint.  With 32-row chunks the stacked operands
 // [At; Rt], [Bt; Kt], [A_ak; A_rk] and [T; A_rb] have 64 rows, so every product is a natural
-// M=64 MMA (no padding rows), one CTA needs 94 KB of shared memory and 256 TMEM columns, and
-// two CTAs of 256 threads (<= 128 registers) share an SM: while one waits for its MMAs or a
+// M=64 MMA (no padding rows), one CTA needs 112 KB of shared memory and 256 TMEM columns, and
+// two CTAs of 288 threads (96 registers) share an SM: while one waits for its MMAs or a
 // barrier the other one's CUDA-core phases run.  A 64-row accumulator of an M=64 MMA puts row i
-// in TMEM lane 32*(i/16) + i%16, i.e. every warp quadrant holds 16 rows in its lanes 0..15.
+// in TMEM lane 32*(i/16) + i%16, i.e. every warp quadrant holds 16 rows in its lanes 0..15; the
+// read-backs use the 16x256b fragment shape, which spreads those 16 rows over all 32 threads.
+// Eight warps compute; a ninth issues every MMA and TMA load (see the loop below).
 //
 // Per chunk of L <= 32 rows (g_t = inclusive cumulative retention inside the chunk):
 //     P  = [At; Rt] [Bt; Kt]^T  (64x64) -> A_ab, A_ak (strictly lower), A_rb, A_rk (lower), 32x32 each
