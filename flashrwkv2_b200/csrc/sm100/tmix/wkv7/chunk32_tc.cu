@@ -93,7 +93,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_sum + kWarps * 64);
   uint64_t* bar_mma = bar_tma + 1;
   uint64_t* bar_state = bar_tma + 2;  // its own barrier: two commits may not complete two phases of one
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_state + 1);
+  uint64_t* bar_drain = bar_tma + 3;  // the issuer warp's last commit: every MMA has retired before TMEM is freed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_drain + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;  // set by the compute warps when a bounded wait gave up
   const uint32_t sbase = smem_u32(smem);
 
@@ -101,6 +102,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     mbar_init(bar_tma, 1);
     mbar_init(bar_mma, 1);
     mbar_init(bar_state, 1);
+    mbar_init(bar_drain, 1);
     mbar_fence_init();
     *abort_flag = 0u;
     tma_prefetch_descriptor(&maps.r);
@@ -600,7 +602,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (lane == 0) {
         tcgen05_fence_after_sync();
         issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
-        mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
+        if (c != p.skip_commit_chunk) mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
         issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
         if (c + 1 < n_chunks) issue_tma(c + 1);  // a whole chunk ahead of its use; after the MMAs, which are waited for
       }
@@ -630,6 +632,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
       __syncwarp();
     }
+    // every MMA of this CTA has retired before anybody frees its TMEM (matters after an abort only: otherwise the
+    // compute warps have waited for the last state update)
+    if (lane == 0) {
+      mma_commit(bar_drain);
+      mbar_wait(bar_drain, 0);
+    }
+    __syncwarp();
   }
 
   if (failed) {
@@ -662,7 +671,8 @@ int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* st
   chunk::Maps maps;
   const int map_rc = chunk::make_maps(&maps, r, w, k, v, a, b, total_tokens, heads, bf16, kChunk);
   if (map_rc != FRWKV_OK) return map_rc;
-  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from};
+  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from,
+                       chunk::test_skip_commit_chunk()};
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
   if (bf16) return launch_typed32<__nv_bfloat16>(p, maps, logits, stream);
   return launch_typed32<__half>(p, maps, logits, stream);

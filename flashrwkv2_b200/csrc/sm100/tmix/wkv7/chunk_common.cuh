@@ -28,6 +28,13 @@ __device__ long long g_phase_ticks[16];
 #define FRWKV_PHASE(i)
 #endif
 
+// Test hook for the bounded waits: FRWKV_TEST_SKIP_COMMIT=<chunk index> makes the 32-row kernel leave out one
+// tcgen05.commit, so that the wait on it runs out and the failure path (error flag, no hang) can be exercised.
+inline int test_skip_commit_chunk() {
+  const char* e = std::getenv("FRWKV_TEST_SKIP_COMMIT");
+  return e != nullptr ? std::atoi(e) : -1;
+}
+
 struct ChunkParams {
   const int* cu;
   const int* slots;
@@ -41,6 +48,7 @@ struct ChunkParams {
   float scale;
   const int* order;  // CTA rank -> sequence, longest first (nullptr: natural order)
   int len_from;      // > 0: only sequences at least this long (shorter ones go to the recurrence kernel)
+  int skip_commit_chunk;  // test hook (FRWKV_TEST_SKIP_COMMIT): chunk whose first MMA commit is left out, -1 = none
 };
 
 struct Maps {

@@ -652,7 +652,7 @@ int launch_chunk64_tc(const int32_t* cu, const int32_t* slots, const int32_t* st
   Maps maps;
   const int map_rc = make_maps(&maps, r, w, k, v, a, b, total_tokens, heads, bf16, kChunk);
   if (map_rc != FRWKV_OK) return map_rc;
-  ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from};
+  ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from, -1};
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
   if (bf16) return launch_typed<__nv_bfloat16>(p, maps, logits, stream);
   return launch_typed<__half>(p, maps, logits, stream);

@@ -246,3 +246,15 @@ def test_auto_strategy_splits_a_mixed_batch_by_length():
     cu = case["cu_seqlens"].tolist()
     short_rows = torch.cat([torch.arange(cu[i], cu[i + 1]) for i, n in enumerate(lengths) if n < 16])
     assert max_err_over_rms(y32[short_rows], y_ref[short_rows]) <= 1e-5
+
+
+def test_bounded_wait_reports_instead_of_hanging(monkeypatch):
+    """A tcgen05.commit that never comes (test hook FRWKV_TEST_SKIP_COMMIT): the waiting warps give up after about
+    a second, the CTA raises the error flag and leaves in order (every warp, the MMA-issuing one included), and the
+    device stays usable for the next call."""
+    case = _random_case((96, 40), 2, torch.bfloat16, seed=31)
+    monkeypatch.setenv("FRWKV_TEST_SKIP_COMMIT", "1")
+    _, _, _, err = _run_tc(case)
+    assert int(err.item()) == 1
+    monkeypatch.delenv("FRWKV_TEST_SKIP_COMMIT")
+    _check(case, *_run_tc(case))
