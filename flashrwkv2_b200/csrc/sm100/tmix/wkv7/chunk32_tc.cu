@@ -237,7 +237,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   // MMAs of chunk c still read, stay in these registers until release_operands().
   uint32_t held_x2[16];  // per row of this thread: Bt hi, Bt lo, Kt hi, Kt lo
   uint4 held_v_hi, held_v_lo = make_uint4(0u, 0u, 0u, 0u);
-  auto prepare_operands = [&](int chunk, float* gamma_dst) -> bool {  // all threads; one CTA barrier inside
+  float2 held_lg[kChunk / kWarps];  // log2 of the inclusive decay product of this thread's rows, scan -> scaling
+  float2 held_off = make_float2(0.f, 0.f);  // ... and of the rows before them
+  auto scan_decay = [&](int chunk) -> bool {  // first half (all compute threads; one compute barrier inside)
     const int rows = min(kChunk, len - chunk * kChunk);
     const bool ok = mbar_wait(bar_tma, tma_parity);
     tma_in_flight = false;
@@ -245,11 +247,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     constexpr int kRowsPerWarp = kChunk / kWarps;  // 4
     const int kp = lane;                           // key channels 2*kp, 2*kp+1
     const int tg = warp;                           // rows 4*tg .. 4*tg+3
-    const uint32_t* raw_r = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 0 * kRawTile);
     const uint32_t* raw_w = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 1 * kRawTile);
-    const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
-    const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
-    const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
     float2 bias2 = make_float2(0.f, 0.f);
     if (bias_g != nullptr) bias2 = make_float2(to_f32(bias_g[2 * kp]), to_f32(bias_g[2 * kp + 1]));
     float2 run = make_float2(0.f, 0.f);
@@ -302,13 +300,26 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         off.y += sgrp.y;
       }
     }
-    float2 g_prev = make_float2(fast_exp2(off.x), fast_exp2(off.y));
+    held_off = off;
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) held_lg[i] = make_float2(off.x + cum[i].x, off.y + cum[i].y);
+    return ok;
+  };
+  auto scale_operands = [&](int chunk, float* gamma_dst) {  // second half: no barrier inside
+    const int rows = min(kChunk, len - chunk * kChunk);
+    constexpr int kRowsPerWarp = kChunk / kWarps;
+    const int kp = lane, tg = warp;
+    const uint32_t* raw_r = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 0 * kRawTile);
+    const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
+    const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
+    const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
+    float2 g_prev = make_float2(fast_exp2(held_off.x), fast_exp2(held_off.y));
     uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kStride64 + (kp & 3) * 4;
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; ++i) {
       const int t = tg * kRowsPerWarp + i;
       const bool live = t < rows;
-      const float2 lg = make_float2(off.x + cum[i].x, off.y + cum[i].y);
+      const float2 lg = held_lg[i];
       const float2 g = make_float2(fast_exp2(lg.x), fast_exp2(lg.y));
       const float2 gi = make_float2(fast_exp2(-lg.x), fast_exp2(-lg.y));
       const float2 gx = g_prev;  // exclusive product = inclusive product of the previous row
@@ -333,7 +344,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       split2(k2.x * gi.x, k2.y * gi.y, held_x2[4 * i + 2], held_x2[4 * i + 3]);
       if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_dst)[kp] = g;
     }
-    return ok;
   };
   auto release_operands = [&]() {  // [Bt; Kt] and V of the prepared chunk: registers -> tiles
     const int kp = lane, tg = warp;
@@ -364,7 +374,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     // warp, which reads `abort_flag` after the first hand-off of each chunk, always gets out of its barriers.
     // =====================================================================================================
     // chunk 0 is prepared up front; afterwards every chunk prepares its successor
-    bad |= !prepare_operands(0, gamma_l);
+    bad |= !scan_decay(0);
+    scale_operands(0, gamma_l);
     release_operands();
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
@@ -508,6 +519,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       named_arrive(kBarInverse, kThreads);  // -> U = T W (rows 32..63 of this product are unused)
       FRWKV_PHASE(5)
 
+      // while U is computed: first half of the next chunk's operand preparation (decay scan)
+      if (!failed && c + 1 < n_chunks) bad |= !scan_decay(c + 1);
       if (!failed) {
         bad |= !mbar_wait(bar_mma, mma_phase & 1);
         tcgen05_fence_after_sync();
@@ -520,8 +533,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       named_arrive(kBarU, kThreads);  // -> Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V
       FRWKV_PHASE(7)
 
-      // the tensor pipe is busy with Y and S: prepare the next chunk's operands meanwhile
-      if (!failed && c + 1 < n_chunks) bad |= !prepare_operands(c + 1, gamma_l + ((c + 1) & 1) * 64);
+      // the tensor pipe is busy with Y and S: second half of the next chunk's operand preparation meanwhile
+      if (!failed && c + 1 < n_chunks) scale_operands(c + 1, gamma_l + ((c + 1) & 1) * 64);
       FRWKV_PHASE(1)
       if (!failed) {
         bad |= !mbar_wait(bar_mma, mma_phase & 1);
