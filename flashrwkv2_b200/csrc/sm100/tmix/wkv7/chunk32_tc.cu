@@ -25,9 +25,9 @@ using namespace chunk;
 constexpr int kWarps = 8;                       // compute warps
 constexpr int kComputeThreads = kWarps * 32;    // 256
 constexpr int kThreads = kComputeThreads + 32;  // + one warp that issues every MMA and TMA load
-// named barriers (0 is __syncthreads): the compute warps' own barrier, and four hand-offs on which the compute
+// named barriers (0 is __syncthreads): the compute warps' own barrier, and five hand-offs on which the compute
 // threads arrive (without waiting) and the issuer warp waits
-constexpr int kBarCompute = 1, kBarOperands = 2, kBarMasks = 3, kBarInverse = 4, kBarU = 5;
+constexpr int kBarCompute = 1, kBarOperands = 2, kBarState = 3, kBarMasks = 4, kBarInverse = 5, kBarU = 6;
 constexpr int kChunk = 32;
 
 // ---- shared-memory map (bytes) -------------------------------------------------------------
@@ -369,9 +369,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   if (compute_warp) {
     // =====================================================================================================
     // Compute warps.  They never wait for the issuer warp except through the MMA mbarriers (bounded waits);
-    // at each hand-off they arrive on a named barrier and go on.  Once a wait has given up (`failed`, agreed on
-    // at a compute barrier) they skip all work but still make every arrival of the chunk, so that the issuer
-    // warp, which reads `abort_flag` after the first hand-off of each chunk, always gets out of its barriers.
+    // at each hand-off they arrive on a named barrier and go on.  A wait that gave up sets `bad`; the compute
+    // warps agree on it at their next own barrier (`failed`), set `abort_flag`, make the one arrival the issuer
+    // warp may still be waiting for, and leave.  The issuer warp reads `abort_flag` after every hand-off, so it
+    // is never left waiting.
     // =====================================================================================================
     // chunk 0 is prepared up front; afterwards every chunk prepares its successor
     bad |= !scan_decay(0);
@@ -381,14 +382,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tcgen05_fence_before_sync();
     failed = named_sync_or(kBarCompute, kComputeThreads, bad);
     if (failed && tid == 0) *abort_flag = 1u;
+    named_arrive(kBarOperands, kThreads);  // [At; Rt], [Bt; Kt], V of chunk 0 are in place -> P
+    if (!failed) {
+      named_arrive(kBarState, kThreads);   // ... and so is S0 -> Q, then the next chunk's load
+      if (n_chunks > 1) tma_in_flight = true;
+    }
 
-    for (int c = 0; c < n_chunks; ++c) {
+    for (int c = 0; c < n_chunks && !failed; ++c) {
       const int rows = min(kChunk, len - c * kChunk);
       const int row0 = t_begin + c * kChunk;
-      // ---- hand-off: [At; Rt], [Bt; Kt], V and S0 of chunk c are in place; the staging area is free ----
-      named_arrive(kBarOperands, kThreads);
-      if (failed) break;
-      if (c + 1 < n_chunks) tma_in_flight = true;  // the issuer warp loads the next chunk's tokens now
       FRWKV_PHASE(0)
 
       // ================= P = X1 X2^T (the issuer warp also starts Q = X1 S0, which runs under the read-back) ====
@@ -432,10 +434,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       tcgen05_fence_before_sync();
       named_arrive(kBarMasks, kThreads);  // -> Q += [A_ak; A_rk] V
       failed = named_sync_or(kBarCompute, kComputeThreads, bad);  // A_ab scratch visible to the inverse
+      if (failed) {
+        if (tid == 0) *abort_flag = 1u;
+        named_arrive(kBarInverse, kThreads);  // the issuer warp's next hand-off
+        break;
+      }
       FRWKV_PHASE(3)
 
       // ================= 32x32 inverse on CUDA cores while Q is finished by the tensor pipe =================
-      if (!failed) {
+      {
         float* ab = reinterpret_cast<float*>(smem + kOffAb);
         float* ti = reinterpret_cast<float*>(smem + kOffTi);
         float* mb = reinterpret_cast<float*>(smem + kOffMb);
@@ -507,12 +514,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
           *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
         }
       }
-      else {
-        ++mma_phase;
-        named_sync(kBarCompute, kComputeThreads);
-        named_sync(kBarCompute, kComputeThreads);
-        named_sync(kBarCompute, kComputeThreads);
-      }
       FRWKV_PHASE(4)
       fence_proxy_async_smem();
       tcgen05_fence_before_sync();
@@ -520,86 +521,94 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       FRWKV_PHASE(5)
 
       // while U is computed: first half of the next chunk's operand preparation (decay scan)
-      if (!failed && c + 1 < n_chunks) bad |= !scan_decay(c + 1);
-      if (!failed) {
-        bad |= !mbar_wait(bar_mma, mma_phase & 1);
-        tcgen05_fence_after_sync();
-        FRWKV_PHASE(6)
-        rows_to_operand(kColU);
-      }
+      if (c + 1 < n_chunks) bad |= !scan_decay(c + 1);
+      bad |= !mbar_wait(bar_mma, mma_phase & 1);
       ++mma_phase;
+      tcgen05_fence_after_sync();
+      FRWKV_PHASE(6)
+      rows_to_operand(kColU);
       fence_proxy_async_smem();
       tcgen05_fence_before_sync();
       named_arrive(kBarU, kThreads);  // -> Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V
       FRWKV_PHASE(7)
 
       // the tensor pipe is busy with Y and S: second half of the next chunk's operand preparation meanwhile
-      if (!failed && c + 1 < n_chunks) scale_operands(c + 1, gamma_l + ((c + 1) & 1) * 64);
+      if (c + 1 < n_chunks) scale_operands(c + 1, gamma_l + ((c + 1) & 1) * 64);
       FRWKV_PHASE(1)
-      if (!failed) {
-        bad |= !mbar_wait(bar_mma, mma_phase & 1);
-        tcgen05_fence_after_sync();
-        FRWKV_PHASE(8)
-        // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
-        if (quad >= 2) {
-          uint32_t regs[16];
-          tmem_ld_frag16(tmem_lane + kColQ + half * 32, regs);
-          tmem_ld_wait();
+      bad |= !mbar_wait(bar_mma, mma_phase & 1);
+      ++mma_phase;
+      tcgen05_fence_after_sync();
+      FRWKV_PHASE(8)
+      // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
+      if (quad >= 2) {
+        uint32_t regs[16];
+        tmem_ld_frag16(tmem_lane + kColQ + half * 32, regs);
+        tmem_ld_wait();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int t = frow0 + 8 * h - 32;
+          if (t < rows) {
+            const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
+            io_t* yp = static_cast<io_t*>(p.y) + out;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+              const float y0 = __uint_as_float(regs[4 * n + 2 * h]) * p.scale;
+              const float y1 = __uint_as_float(regs[4 * n + 2 * h + 1]) * p.scale;
+              alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
+              *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
+              if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
+            }
+          }
+        }
+      }
+      bad |= !mbar_wait(bar_state, c & 1);
+      tcgen05_fence_after_sync();
+      // This thread has seen the state MMAs finish: their [Bt; Kt] and V tiles take the next chunk's values, and
+      // the next chunk's P = X1 X2^T, which does not need the state, starts while the state is read back.
+      if (c + 1 < n_chunks) {
+        release_operands();
+        fence_proxy_async_smem();
+        named_arrive(kBarOperands, kThreads);
+      }
+      // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
+      {
+        uint32_t regs[16];
+        tmem_ld_frag16(tmem_lane + kColS + half * 32, regs);
+        tmem_ld_wait();
+        const float* gamma_c = gamma_l + (c & 1) * 64;
+        const float gl[2] = {gamma_c[frow0], gamma_c[frow0 + 8]};
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          x[i] = __uint_as_float(regs[i]) * gl[(i >> 1) & 1];
+          regs[i] = __float_as_uint(x[i]);
+        }
+        if (c + 1 < n_chunks) {
+          tmem_st_frag16(tmem_lane + kColS + half * 32, regs);
+          store_operand_frag(kOffOp, kTileK64, half * 4, x);
+          tmem_st_wait();
+        } else {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const int t = frow0 + 8 * h - 32;
-            if (t < rows) {
-              const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
-              io_t* yp = static_cast<io_t*>(p.y) + out;
+            float* dst = state_g + (frow0 + 8 * h) * kHeadDim + half * 32 + 2 * fq;
 #pragma unroll
-              for (int n = 0; n < 4; ++n) {
-                const float y0 = __uint_as_float(regs[4 * n + 2 * h]) * p.scale;
-                const float y1 = __uint_as_float(regs[4 * n + 2 * h + 1]) * p.scale;
-                alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
-                *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
-                if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
-              }
-            }
+            for (int n = 0; n < 4; ++n)
+              __stcs(reinterpret_cast<float2*>(dst + 8 * n), make_float2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1]));
           }
         }
-        bad |= !mbar_wait(bar_state, c & 1);
-        tcgen05_fence_after_sync();
-        // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
-        {
-          uint32_t regs[16];
-          tmem_ld_frag16(tmem_lane + kColS + half * 32, regs);
-          tmem_ld_wait();
-          const float* gamma_c = gamma_l + (c & 1) * 64;
-          const float gl[2] = {gamma_c[frow0], gamma_c[frow0 + 8]};
-          float x[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            x[i] = __uint_as_float(regs[i]) * gl[(i >> 1) & 1];
-            regs[i] = __float_as_uint(x[i]);
-          }
-          if (c + 1 < n_chunks) {
-            tmem_st_frag16(tmem_lane + kColS + half * 32, regs);
-            store_operand_frag(kOffOp, kTileK64, half * 4, x);
-            tmem_st_wait();
-          } else {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              float* dst = state_g + (frow0 + 8 * h) * kHeadDim + half * 32 + 2 * fq;
-#pragma unroll
-              for (int n = 0; n < 4; ++n)
-                __stcs(reinterpret_cast<float2*>(dst + 8 * n), make_float2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1]));
-            }
-          }
-        }
-        // this thread has seen the state MMAs finish: their [Bt; Kt] and V tiles may take the next chunk's values
-        if (c + 1 < n_chunks) release_operands();
       }
-      ++mma_phase;
-      fence_proxy_async_smem();
-      tcgen05_fence_before_sync();
-      failed |= named_sync_or(kBarCompute, kComputeThreads, bad);
-      if (failed && tid == 0) *abort_flag = 1u;  // before the next arrival on kBarOperands
-      tcgen05_fence_after_sync();
+      if (c + 1 < n_chunks) {
+        fence_proxy_async_smem();
+        tcgen05_fence_before_sync();
+        named_arrive(kBarState, kThreads);  // S0 of the next chunk is in place -> Q, then the load after next
+        if (c + 2 < n_chunks) tma_in_flight = true;
+      }
+      failed = named_sync_or(kBarCompute, kComputeThreads, bad);
+      if (failed) {
+        if (tid == 0) *abort_flag = 1u;
+        if (c + 1 < n_chunks) named_arrive(kBarMasks, kThreads);  // the issuer warp's next hand-off
+        break;
+      }
       FRWKV_PHASE(9)
     }
   } else {
@@ -607,7 +616,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     // Issuer warp: lane 0 issues every TMA load and every MMA, in the order the results are needed (the tensor
     // pipe runs them first in, first out).  An issuing thread stalls while the MMA queue is full, at about the
     // rate the MMAs execute, so none of the compute warps issues anything.  The warp waits on named barriers
-    // only; the compute warps make every arrival of a chunk even after a failure.
+    // only and leaves when it finds `abort_flag` set after one of them.
     // =====================================================================================================
     for (int c = 0; c < n_chunks; ++c) {
       named_sync(kBarOperands, kThreads);
@@ -615,12 +624,19 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (lane == 0) {
         tcgen05_fence_after_sync();
         issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
-        if (c != p.skip_commit_chunk) mma_commit(bar_mma);  // P only: Q = X1 S0 executes while P is read back
-        issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);
+        if (c != p.skip_commit_chunk) mma_commit(bar_mma);  // P: runs while the previous chunk's state is read back
+      }
+      __syncwarp();
+      named_sync(kBarState, kThreads);
+      if (*abort_flag != 0u) break;
+      if (lane == 0) {
+        tcgen05_fence_after_sync();
+        issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);  // Q = X1 S0: under the P read-back
         if (c + 1 < n_chunks) issue_tma(c + 1);  // a whole chunk ahead of its use; after the MMAs, which are waited for
       }
       __syncwarp();
       named_sync(kBarMasks, kThreads);
+      if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
         issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
@@ -628,6 +644,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
       __syncwarp();
       named_sync(kBarInverse, kThreads);
+      if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
         issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
@@ -635,6 +652,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
       __syncwarp();
       named_sync(kBarU, kThreads);
+      if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
         issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
