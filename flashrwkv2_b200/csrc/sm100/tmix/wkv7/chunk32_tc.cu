@@ -8,7 +8,9 @@
 // barrier the other one's CUDA-core phases run.  A 64-row accumulator of an M=64 MMA puts row i
 // in TMEM lane 32*(i/16) + i%16, i.e. every warp quadrant holds 16 rows in its lanes 0..15; the
 // read-backs use the 16x256b fragment shape, which spreads those 16 rows over all 32 threads.
-// Eight warps compute; a ninth issues every MMA and TMA load (see the loop below).
+// Eight warps compute; a ninth issues every MMA and TMA load (see the loop below).  Inside the stacked operands the
+// two kinds of rows alternate in groups of eight (token t: 16*(t/8) + t%8 and eight further), so that every
+// thread's fragment holds one row of each kind and all eight warps share every read-back.
 //
 // Per chunk of L <= 32 rows (g_t = inclusive cumulative retention inside the chunk):
 //     P  = [At; Rt] [Bt; Kt]^T  (64x64) -> A_ab, A_ak (strictly lower), A_rb, A_rk (lower), 32x32 each
@@ -212,15 +214,22 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   const Operand op_bt = make_operand(sbase + kOffX2, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
   const Operand op_kt = make_operand(sbase + kOffX2 + 4 * kRowGroup, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
 
-  auto rows_to_operand = [&](uint32_t col) {  // accumulator rows 0..31 x 64 columns at `col` -> kOffOp
-    if (quad < 2) {
-      uint32_t regs[16];
-      tmem_ld_frag16(tmem_lane + col + half * 32, regs);
-      tmem_ld_wait();
-      float x[16];
+  // Row order of the stacked 64-row operands [At; Rt], [A_ak; A_rk], [T; A_rb] and of their accumulators: the two
+  // kinds alternate in groups of eight, token t's At-kind row at 16*(t/8) + t%8 and its Rt-kind row eight further.
+  // A quadrant then holds eight rows of each kind, and in the fragment view every thread has one of each (rows
+  // frow0 and frow0 + 8, both of token ftok): W, U and y read-backs are spread over all eight compute warps.
+  const int ftok = quad * 8 + (lane >> 2);
+  auto rows_to_operand = [&](uint32_t col) {  // the 32 At-kind accumulator rows x 64 columns at `col` -> kOffOp (row = token)
+    uint32_t regs[16];
+    tmem_ld_frag16(tmem_lane + col + half * 32, regs);
+    tmem_ld_wait();
+    uint8_t* dst = smem + kOffOp + (ftok >> 3) * kRowGroup + (ftok & 7) * 16 + fq * 4;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) x[i] = __uint_as_float(regs[i]);
-      store_operand_frag(kOffOp, kTileK64, half * 4, x);
+    for (int n = 0; n < 4; ++n) {
+      uint32_t hi, lo;
+      split2(__uint_as_float(regs[4 * n]), __uint_as_float(regs[4 * n + 1]), hi, lo);
+      *reinterpret_cast<uint32_t*>(dst + (half * 4 + n) * kStride64) = hi;
+      *reinterpret_cast<uint32_t*>(dst + kTileK64 + (half * 4 + n) * kStride64) = lo;
     }
   };
 
@@ -331,15 +340,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (!live) {
         r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
       }
-      const uint32_t row_lo = (t >> 3) * kRowGroup + (t & 7) * 16;         // rows 0..31
-      const uint32_t row_hi = ((t + 32) >> 3) * kRowGroup + (t & 7) * 16;  // rows 32..63
+      const uint32_t row_a = 2 * (t >> 3) * kRowGroup + (t & 7) * 16;  // At row of token t: 16*(t/8) + t%8
+      const uint32_t row_r = row_a + kRowGroup;                        // Rt row: eight further
       uint32_t h, l;
       split2(a2.x * gx.x, a2.y * gx.y, h, l);
-      *reinterpret_cast<uint32_t*>(x1 + row_lo) = h;
-      *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_lo) = l;
+      *reinterpret_cast<uint32_t*>(x1 + row_a) = h;
+      *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_a) = l;
       split2(r2.x * g.x, r2.y * g.y, h, l);
-      *reinterpret_cast<uint32_t*>(x1 + row_hi) = h;
-      *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_hi) = l;
+      *reinterpret_cast<uint32_t*>(x1 + row_r) = h;
+      *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_r) = l;
       split2(b2.x * gi.x, b2.y * gi.y, held_x2[4 * i], held_x2[4 * i + 1]);
       split2(k2.x * gi.x, k2.y * gi.y, held_x2[4 * i + 2], held_x2[4 * i + 3]);
       if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_dst)[kp] = g;
@@ -400,16 +409,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       FRWKV_PHASE(2)
       // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
       {
-        // accumulator row arow: rows 0..31 belong to At (quadrants 0,1), rows 32..63 to Rt (quadrants 2,3);
-        // columns 32*half..: half 0 = products with Bt (A_ab / A_rb), half 1 = with Kt (A_ak / A_rk)
+        // this thread's rows: h = 0 the At row of token ftok (products with Bt: A_ab, with Kt: A_ak; strictly lower),
+        // h = 1 its Rt row (A_rb, A_rk; lower); columns 32*half..: half 0 = products with Bt, half 1 = with Kt
         uint32_t regs[16];
         tmem_ld_frag16(tmem_lane + kColP + half * 32, regs);
         tmem_ld_wait();
         float vals[16];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int t = (frow0 + 8 * h) & 31;
-          const int limit = quad < 2 ? t : t + 1;  // keep columns s < limit
+          const int limit = ftok + h;  // keep columns s < limit
 #pragma unroll
           for (int n = 0; n < 4; ++n) {
 #pragma unroll
@@ -417,17 +425,21 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
               vals[4 * n + 2 * h + e] = 8 * n + 2 * fq + e < limit ? __uint_as_float(regs[4 * n + 2 * h + e]) : 0.0f;
           }
         }
-        if (quad < 2 && half == 0) {  // A_ab -> fp32 scratch for the inverse
+        if (half == 0) {
+          // A_ab row -> fp32 scratch of the inverse; A_rb row -> [T; A_rb] at its accumulator position
+          float* ab_row = reinterpret_cast<float*>(smem + kOffAb) + ftok * kInvLd + 2 * fq;
+          const int row = frow0 + 8;
+          uint8_t* rb = smem + kOffX4 + (row >> 3) * kRowGroup + (row & 7) * 16 + fq * 4;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float* dst = reinterpret_cast<float*>(smem + kOffAb) + (frow0 + 8 * h) * kInvLd + 2 * fq;
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-              *reinterpret_cast<float2*>(dst + 8 * n) = make_float2(vals[4 * n + 2 * h], vals[4 * n + 2 * h + 1]);
+          for (int n = 0; n < 4; ++n) {
+            *reinterpret_cast<float2*>(ab_row + 8 * n) = make_float2(vals[4 * n], vals[4 * n + 1]);
+            uint32_t hi, lo;
+            split2(vals[4 * n + 2], vals[4 * n + 3], hi, lo);
+            *reinterpret_cast<uint32_t*>(rb + n * kStride64) = hi;
+            *reinterpret_cast<uint32_t*>(rb + kTileK32 + n * kStride64) = lo;
           }
         } else {
-          // half 1: A_ak -> X3 rows 0..31 (quad<2), A_rk -> X3 rows 32..63; half 0, quad>=2: A_rb -> X4 rows 32..63
-          store_operand_frag(half == 1 ? kOffX3 : kOffX4, kTileK32, 0, vals);
+          store_operand_frag(kOffX3, kTileK32, 0, vals);  // A_ak and A_rk rows, in accumulator order
         }
       }
       fence_proxy_async_smem();
@@ -447,9 +459,8 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         float* ti = reinterpret_cast<float*>(smem + kOffTi);
         float* mb = reinterpret_cast<float*>(smem + kOffMb);
         bool w_ready = true;
-        // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread, on a warp
-        // that has no accumulator rows to read back; meanwhile the warps of quadrants 0,1 wait for Q and
-        // turn W = Q rows 0..31 into the operand tile, and the remaining warps clear T's upper block
+        // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread, on one warp;
+        // meanwhile the others wait for Q and turn its At-kind rows (W) into the operand tile
         if (warp == 2) {
           const int d = lane >> 4, j = lane & 15;
           const float* blk = ab + (16 * d) * kInvLd + 16 * d;
@@ -463,12 +474,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
             for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
           }
-        } else if (quad >= 2) {  // warps 3, 6, 7: nothing to do until level 1
-        } else {
-          w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_phase & 1));
-          tcgen05_fence_after_sync();
-          if (w_ready) rows_to_operand(kColQ);
         }
+        w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_phase & 1));
+        tcgen05_fence_after_sync();
+        if (w_ready) rows_to_operand(kColQ);
         ++mma_phase;
         bad |= !w_ready;
         named_sync(kBarCompute, kComputeThreads);
@@ -500,7 +509,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         }
         named_sync(kBarCompute, kComputeThreads);
         FRWKV_PHASE(11)
-        // T -> rows 0..31 of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
+        // T -> the At-kind rows of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
         if (tid < 128) {
           const int t = tid >> 2, cj = tid & 3;
           float4 f0 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8);
@@ -509,7 +518,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
           const float x[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
           uint4 hi, lo;
           split8(x, hi, lo);
-          uint8_t* dst = smem + kOffX4 + (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64;
+          uint8_t* dst = smem + kOffX4 + 2 * (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64;  // At-kind row of token t
           *reinterpret_cast<uint4*>(dst) = hi;
           *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
         }
@@ -539,25 +548,21 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       ++mma_phase;
       tcgen05_fence_after_sync();
       FRWKV_PHASE(8)
-      // ---- y rows: accumulator rows 32..63 of Q (quadrants 2,3) ----
-      if (quad >= 2) {
+      // ---- y rows: the Rt-kind rows of Q (h = 1 of every thread) ----
+      {
         uint32_t regs[16];
         tmem_ld_frag16(tmem_lane + kColQ + half * 32, regs);
         tmem_ld_wait();
+        if (ftok < rows) {
+          const size_t out = (static_cast<size_t>(row0 + ftok) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
+          io_t* yp = static_cast<io_t*>(p.y) + out;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int t = frow0 + 8 * h - 32;
-          if (t < rows) {
-            const size_t out = (static_cast<size_t>(row0 + t) * p.heads + head) * kHeadDim + half * 32 + 2 * fq;
-            io_t* yp = static_cast<io_t*>(p.y) + out;
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-              const float y0 = __uint_as_float(regs[4 * n + 2 * h]) * p.scale;
-              const float y1 = __uint_as_float(regs[4 * n + 2 * h + 1]) * p.scale;
-              alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
-              *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
-              if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
-            }
+          for (int n = 0; n < 4; ++n) {
+            const float y0 = __uint_as_float(regs[4 * n + 2]) * p.scale;
+            const float y1 = __uint_as_float(regs[4 * n + 3]) * p.scale;
+            alignas(4) io_t packed[2] = {from_f32<io_t>(y0), from_f32<io_t>(y1)};
+            *reinterpret_cast<uint32_t*>(yp + 8 * n) = *reinterpret_cast<const uint32_t*>(packed);
+            if (p.y_f32 != nullptr) *reinterpret_cast<float2*>(p.y_f32 + out + 8 * n) = make_float2(y0, y1);
           }
         }
       }
