@@ -15,14 +15,15 @@ using namespace tc;
 
 constexpr uint32_t kRowGroup = 128;  // one core-matrix row group: 8 rows x 16 B
 
-// Optional per-phase cycle counters of CTA 0 (development builds only).
+// Optional per-phase cycle counters of CTA 0 (development builds only).  The add is a reduction without a return
+// value: a plain read-modify-write would stall the measuring warp for a global-memory round trip at every marker.
 #ifdef FRWKV_CHUNK_TIMING
-__device__ long long g_phase_ticks[16];
-#define FRWKV_PHASE(i)                                        \
-  if (tid == 255 && blockIdx.x == 0) {                        \
-    const long long now = clock64();                          \
-    g_phase_ticks[i] += now - phase_t0;                       \
-    phase_t0 = now;                                           \
+__device__ unsigned long long g_phase_ticks[16];
+#define FRWKV_PHASE(i)                                                                  \
+  if (tid == 255 && blockIdx.x == 0) {                                                  \
+    const long long now = clock64();                                                    \
+    atomicAdd(&g_phase_ticks[i], static_cast<unsigned long long>(now - phase_t0));      \
+    phase_t0 = now;                                                                     \
   }
 #else
 #define FRWKV_PHASE(i)
