@@ -33,7 +33,11 @@ extern "C" {
 enum { FRWKV_IO_BF16 = 0, FRWKV_IO_FP16 = 1, FRWKV_IO_FP32 = 2 };
 /* meaning of w: raw decay logits (the reference's contract:
  * rho = exp(-exp(-1/2) * sigmoid(w + bias)), csrc/sm120/tmix/wkv7/recurrent_decay.cuh:18-23)
- * or the retention rho itself (how the benchmark workloads are specified). */
+ * or the retention rho itself (how the benchmark workloads are specified).
+ * RWKV-7 retentions lie in [exp(-exp(-1/2)), 1] = [0.545, 1], which is what the logits form can produce.  The chunked
+ * prefill kernels divide by the running product of rho over one chunk (32 or 64 rows), so in retention mode they need
+ * rho >= 0.26 (64-row chunks) or 0.07 (32-row chunks) to stay inside the fp32 range; the recurrent entry and
+ * FRWKV_PREFILL_RECURRENT take any rho in [0, 1]. */
 enum { FRWKV_DECAY_LOGITS = 0, FRWKV_DECAY_RETENTION = 1 };
 /* metadata error bits written to status[0]; same values as
  * csrc/validation/recurrent_metadata.cu:15-22 */
