@@ -147,6 +147,13 @@ def test_full_size_configurations_match_the_reference_kernels(ref, ours, name):
     decay mode, inputs generated on the device with the benchmark's distributions."""
     from flashrwkv2_b200.workloads import make_workload
 
+    shape = make_workload(name, with_tensors=False)
+    token_bytes = shape.total_tokens * shape.heads * 64 * 2
+    state_bytes = shape.n_seq * shape.heads * 64 * 64 * 4
+    need = 9 * token_bytes + 3 * state_bytes + (2 << 30)  # six inputs, logits, two outputs; three pools; slack
+    free, _ = torch.cuda.mem_get_info()
+    if free < need:
+        pytest.skip(f"needs {need >> 30} GiB of device memory, {free >> 30} GiB free")
     wl = make_workload(name, device=DEV)
     t = wl.tensors
     g = torch.Generator(device=DEV).manual_seed(wl.seed + 100)
