@@ -313,8 +313,8 @@ def run_ours(args, rank, local_rank, world):
                 line["prefill"] = {"error": str(error)}
             try:
                 line["gpu_baseline"] = gpu_baseline(device, sets)
-            except RuntimeError as error:
-                line["gpu_baseline"] = {"error": str(error)}
+            except Exception as error:  # a baseline that cannot load or run must not take the bench line with it
+                line["gpu_baseline"] = {"error": f"{type(error).__name__}: {error}"}
     return line
 
 

@@ -25,7 +25,10 @@ DEV = "cuda"
 
 @pytest.fixture(scope="module")
 def ref():
-    module = load_ref()
+    try:
+        module = load_ref()
+    except (ImportError, OSError) as error:  # built against another torch / CUDA runtime than the one present
+        pytest.skip(f"oracle/_ref/_C_ref.so does not load here: {error}")
     if module is None:
         pytest.skip("oracle/_ref/_C_ref.so was not built (no reference checkout at build time)")
     return module
