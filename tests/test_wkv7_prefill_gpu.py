@@ -258,3 +258,27 @@ def test_bounded_wait_reports_instead_of_hanging(monkeypatch):
     assert int(err.item()) == 1
     monkeypatch.delenv("FRWKV_TEST_SKIP_COMMIT")
     _check(case, *_run_tc(case))
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_random_shapes_against_the_oracle(seed):
+    """Seeded random batches: ragged lengths around the chunk boundaries, odd head counts, both token types, both
+    decay modes, bias, scale, permuted slots in a larger pool.  Each case goes through the tensor-core kernel alone
+    and through the length-splitting default, and must agree with the CPU oracle."""
+    import random
+
+    rng = random.Random(1000 + seed)
+    n_seq = rng.randint(1, 6)
+    special = (1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 95, 96, 97, 127, 128, 129, 160, 257)
+    lengths = tuple(rng.choice(special) if rng.random() < 0.6 else rng.randint(1, 300) for _ in range(n_seq))
+    heads = rng.choice((1, 2, 3, 5))
+    dtype = rng.choice((torch.bfloat16, torch.float16))
+    retention = rng.random() < 0.5
+    pool_slots = n_seq + rng.randint(0, 3)
+    slots = rng.sample(range(pool_slots), n_seq)
+    case = _random_case(lengths, heads, dtype, seed=2000 + seed, slots=slots, pool_slots=pool_slots,
+                        retention=retention, bias=(not retention) and rng.random() < 0.5)
+    case["scale"] = rng.choice((1.0, 0.37))
+    _check(case, *_run_tc(case))
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _check(case, *_run_op(case, op="prefill", strategy="auto", error_flag=err), err)
