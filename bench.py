@@ -356,7 +356,7 @@ def prefill_extra(lib, _lib, device, peaks, stream):
     return out
 
 
-def _cpu_sample(name, wl, budget_s=10.0, use_c=False):
+def _cpu_sample(name, wl, limit_s=10.0, use_c=False):
     """Time the CPU recurrence on a bounded sample of the workload; returns (tokens/s, cores, text)."""
     from oracle import c_oracle
     from oracle.wkv7_oracle import wkv7_oracle
@@ -380,7 +380,7 @@ def _cpu_sample(name, wl, budget_s=10.0, use_c=False):
     fn()  # warm
     done, reps = 0.0, 0
     begin = time.perf_counter()
-    while done < budget_s and reps < 2000:
+    while done < limit_s and reps < 2000:
         fn()
         reps += 1
         done = time.perf_counter() - begin
@@ -393,7 +393,7 @@ def _cpu_sample(name, wl, budget_s=10.0, use_c=False):
 
 def cpu_baseline(name, wl):
     value, cores, sample = _cpu_sample(name, wl, use_c=False)
-    c_value, c_cores, _ = _cpu_sample(name, wl, budget_s=3.0, use_c=True)
+    c_value, c_cores, _ = _cpu_sample(name, wl, limit_s=3.0, use_c=True)
     return {"value": round(value, 1), "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": sample + " (fp32 PyTorch token loop, the reference's CPU path restated)",
             "c_openmp_port": {"value": round(c_value, 1), "cores": c_cores}, "host_cpus": os.cpu_count()}
@@ -479,12 +479,12 @@ def run_reference(args, rank, world):
     wl = make_workload(name, n_seq=per_rank_n) if name in ("c1", "c4_decode") else make_workload(
         name, n_seq=8 if name != "c3" else None, seq_len=256)
     steps_ms = []
-    per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    per_step_limit = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     sample = ""
     values = []
     for i in range(args.warmup + args.steps):
         begin = time.perf_counter()
-        value, cores, sample = _cpu_sample(name, wl, budget_s=per_step_budget, use_c=False)
+        value, cores, sample = _cpu_sample(name, wl, limit_s=per_step_limit, use_c=False)
         if i >= args.warmup:
             values.append(value)
             steps_ms.append((time.perf_counter() - begin) * 1e3)

@@ -15,7 +15,7 @@
  * at k*D+v, updated in place; cu_seqlens [n_seq+1]; slots [n_seq].
  * decay_mode 0: w holds raw decay logits (bias added before the sigmoid);
  * decay_mode 1: w holds the retention itself.
- * The *_f64 entry keeps the state and all sums in double (error budgeting).
+ * The *_f64 entry keeps the state and all sums in double (error analysis).
  */
 #include <math.h>
 #include <stdlib.h>
