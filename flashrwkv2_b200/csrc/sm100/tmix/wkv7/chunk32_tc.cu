@@ -511,7 +511,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         FRWKV_PHASE(11)
         // T -> the At-kind rows of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
         if (tid < 128) {
-          const int t = tid >> 2, cj = tid & 3;
+          const int t = tid & 31, cj = tid >> 5;  // a quarter-warp stores eight consecutive rows: 128 contiguous bytes
           float4 f0 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8);
           float4 f1 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8 + 4);
           if (t < 16 && cj >= 2) f0 = f1 = make_float4(0.f, 0.f, 0.f, 0.f);  // block above the diagonal (holds scratch)
