@@ -30,6 +30,7 @@ constexpr int kThreads = kComputeThreads + 32;  // + one warp that issues every 
 // named barriers (0 is __syncthreads): the compute warps' own barrier, and five hand-offs on which the compute
 // threads arrive (without waiting) and the issuer warp waits
 constexpr int kBarCompute = 1, kBarOperands = 2, kBarState = 3, kBarMasks = 4, kBarInverse = 5, kBarU = 6;
+constexpr int kBarDiag = 7, kBarMerge = 8;  // inside the inverse: warp 2 -> warps 4..7, and among warps 4..7
 constexpr int kChunk = 32;
 
 // ---- shared-memory map (bytes) -------------------------------------------------------------
@@ -459,22 +460,53 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         float* ti = reinterpret_cast<float*>(smem + kOffTi);
         float* mb = reinterpret_cast<float*>(smem + kOffMb);
         bool w_ready = true;
-        // level 0: the two 16x16 diagonal blocks by forward substitution, one column per thread, on one warp;
-        // meanwhile the others wait for Q and turn its At-kind rows (W) into the operand tile
+        // Levels 0 and 1 of the inverse run on five warps while the others only wait for Q:
+        // level 0 (warp 2): the four 8x8 diagonal blocks of (I - A_ab)^-1 by right-looking forward substitution, one
+        // column per lane, 8 steps; level 1 (warps 4..7, after clearing the 8x8 blocks above the diagonal): inside each
+        // 16x16 diagonal block T[8..15, 0..7] = D_1 * (A[8..15, 0..7] * D_0), 64 outputs per block.
         if (warp == 2) {
-          const int d = lane >> 4, j = lane & 15;
-          const float* blk = ab + (16 * d) * kInvLd + 16 * d;
-          float part[16];  // right-looking substitution: part[t] collects the row sums as columns finish
+          const int o = 8 * (lane >> 3), j = lane & 7;
+          const float* blk = ab + o * kInvLd + o;
+          float part[8];  // part[t] collects the row sums as columns finish
 #pragma unroll
-          for (int t = 0; t < 16; ++t) part[t] = t == j ? 1.0f : 0.0f;
+          for (int t = 0; t < 8; ++t) part[t] = t == j ? 1.0f : 0.0f;
 #pragma unroll
-          for (int s2 = 0; s2 < 16; ++s2) {
+          for (int s2 = 0; s2 < 8; ++s2) {
             const float xs = part[s2];  // x[s2] is final: every earlier column has been folded in
-            ti[(16 * d + s2) * kInvLd + 16 * d + j] = xs;
+            ti[(o + s2) * kInvLd + o + j] = xs;
 #pragma unroll
-            for (int t = s2 + 1; t < 16; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
+            for (int t = s2 + 1; t < 8; ++t) part[t] = fmaf(blk[t * kInvLd + s2], xs, part[t]);
           }
+          named_arrive(kBarDiag, 32 + 128);
+        } else if (warp >= 4) {
+          const int u = tid - 128;
+          const int o = 16 * (u >> 6), r8 = (u >> 3) & 7, c8 = u & 7;
+          float* m8 = mb + 8 * (u >> 6);  // 8x8 scratch of this block inside T's (zero) upper-right block
+          ti[(o + r8) * kInvLd + o + 8 + c8] = 0.0f;
+          named_sync(kBarDiag, 32 + 128);  // warp 2's diagonal blocks are in place
+          float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+          for (int s4 = 0; s4 < 2; ++s4) {
+            const float4 av = *reinterpret_cast<const float4*>(ab + (o + 8 + r8) * kInvLd + o + 4 * s4);
+            acc0 = fmaf(av.x, ti[(o + 4 * s4 + 0) * kInvLd + o + c8], acc0);
+            acc1 = fmaf(av.y, ti[(o + 4 * s4 + 1) * kInvLd + o + c8], acc1);
+            acc0 = fmaf(av.z, ti[(o + 4 * s4 + 2) * kInvLd + o + c8], acc0);
+            acc1 = fmaf(av.w, ti[(o + 4 * s4 + 3) * kInvLd + o + c8], acc1);
+          }
+          m8[r8 * kMbLd + c8] = acc0 + acc1;
+          named_sync(kBarMerge, 128);
+          acc0 = acc1 = 0.0f;
+#pragma unroll
+          for (int s4 = 0; s4 < 2; ++s4) {
+            const float4 dv = *reinterpret_cast<const float4*>(ti + (o + 8 + r8) * kInvLd + o + 8 + 4 * s4);
+            acc0 = fmaf(dv.x, m8[(4 * s4 + 0) * kMbLd + c8], acc0);
+            acc1 = fmaf(dv.y, m8[(4 * s4 + 1) * kMbLd + c8], acc1);
+            acc0 = fmaf(dv.z, m8[(4 * s4 + 2) * kMbLd + c8], acc0);
+            acc1 = fmaf(dv.w, m8[(4 * s4 + 3) * kMbLd + c8], acc1);
+          }
+          ti[(o + 8 + r8) * kInvLd + o + c8] = acc0 + acc1;
         }
+        // meanwhile Q has been finished by the tensor pipe: its At-kind rows (W) become the operand tile
         w_ready = __all_sync(0xffffffffu, mbar_wait(bar_mma, mma_phase & 1));
         tcgen05_fence_after_sync();
         if (w_ready) rows_to_operand(kColQ);
@@ -482,7 +514,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         bad |= !w_ready;
         named_sync(kBarCompute, kComputeThreads);
         FRWKV_PHASE(10)
-        // level 1: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0), one output per thread
+        // level 2: T[16..31, 0..15] = D_1 * (A[16..31, 0..15] * D_0) with the 16x16 blocks, one output per thread
         {
           const int rr = tid >> 4, cc = tid & 15;
           float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four independent partial sums: no 16-deep FMA chain
@@ -637,7 +669,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (lane == 0) {
         tcgen05_fence_after_sync();
         issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);  // Q = X1 S0: under the P read-back
-        if (c + 1 < n_chunks) issue_tma(c + 1);  // a whole chunk ahead of its use; after the MMAs, which are waited for
       }
       __syncwarp();
       named_sync(kBarMasks, kThreads);
@@ -646,6 +677,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         tcgen05_fence_after_sync();
         issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
         mma_commit(bar_mma);  // Q complete (commits track every earlier MMA of the thread)
+        // the next chunk's tokens, most of a chunk ahead of their use; issued here because nothing waits for it,
+        // whereas the products above and below are on the compute warps' critical path
+        if (c + 1 < n_chunks) issue_tma(c + 1);
       }
       __syncwarp();
       named_sync(kBarInverse, kThreads);
