@@ -677,6 +677,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         tcgen05_fence_after_sync();
         issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
         mma_commit(bar_mma);  // Q complete (commits track every earlier MMA of the thread)
+        // S += Kt^T V does not need U: it runs now, while the compute warps invert and the pipe would be idle, instead
+        // of at the end of the chunk where the state products are waited for
+        issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
         // the next chunk's tokens, most of a chunk ahead of their use; issued here because nothing waits for it,
         // whereas the products above and below are on the compute warps' critical path
         if (c + 1 < n_chunks) issue_tma(c + 1);
@@ -697,7 +700,6 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
         mma_commit(bar_mma);  // Y is complete when this one arrives ...
         issue_gemm<true, true, 2>(tmem + kColS, op_bt, op_rows, idesc_mnmn, true);
-        issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
         mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMAs
       }
       __syncwarp();
