@@ -1,33 +1,44 @@
-"""WKV7 benchmark: tokens/s and fraction of roofline on B200, next to the CPU recurrence.
+"""WKV7 benchmark: tokens/s and fraction of roofline on 1/2/4/8 B200, next to the CPU recurrence.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c1|c2|c3|c4_decode|c4_prefill] [--no-extras]
+                    [--workload c4|c1|c2|c3|c4_decode|c4_prefill] [--no-extras] [--no-e2e]
 
-A step is one pass of the hot path over one batch.  The headline workload is the decode
-step (N=256 sequences per GPU, T=1, H=32, D=64, bf16 tokens, fp32 state updated in place).
-With N GPUs every rank runs the same amount of work on its own sequences (weak scaling, no
-collective on the data path); the time is the maximum over ranks, measured with CUDA events.
+Default workload ``c4``: the 7B-width batch sharded by sequence over the N GPUs of one box (strong scaling: the
+total work is fixed, every rank keeps the sequences the longest-first sharder gives it, all sliced from the one
+seeded batch; no collective on the data path).  It has two parts:
+
+  * headline -- decode step, 2048 sequences x 1 token, H=64, D=64, bf16 tokens, fp32 state updated in place
+    (``value``, ``ms_per_step``, ``roofline`` against HBM, ``e2e``, ``clocks``);
+  * ``prefill`` -- 64 sequences x 8192 tokens, H=64, through the tensor-core chunk kernel, a block of the same
+    shape (its own ``value``, ``ms_per_step``, ``roofline`` with the HBM and the tensor fraction, ``clocks``).
+
+A step is one pass of the operator over the batch (one decode launch; one prefill call).  The timed region is K
+steps times R back-to-back repeats, R chosen from the warm-up so that the region lasts at least half a second;
+``ms_per_step`` is per step.  Times are CUDA events, maximum over ranks.  With ``--workload`` one of the single
+configurations is measured instead (also sharded when N > 1).  On one GPU the smaller configurations (c1 decode
+256 x H32, c2 dense prefill 8 x 4096 x H32, c3 ragged prefill) are appended under ``extras`` together with the
+reference's own CUDA kernels on the same GPU.
 
 Keys of the JSON line:
   value      tokens/s with inputs resident in HBM, through the C ABI;
-  e2e        tokens/s through the public Python operator with the six token tensors copied
-             from pinned host memory and y copied back to the host inside the timed region
-             (the state pool is device-resident by contract);
-  roofline   the decode kernel's algorithmic bytes per launch / its average duration, against
-             the measured HBM copy bandwidth;
-  cpu_baseline  the port of the reference's fp32 PyTorch recurrence on the host cores;
-  gpu_baseline  (extra) the reference's own CUDA kernels, built unmodified for sm_100, on this GPU;
-  prefill    (extra) the same figures for the dense prefill workload (8 x 4096 tokens, H=32).
+  e2e        tokens/s through the public Python operator with the six token tensors copied from pinned host
+             memory and y copied back to the host inside the timed region (the state pool is device-resident by
+             contract), plus the host time one operator call takes;
+  roofline   algorithmic bytes per launch / average duration against the measured HBM copy bandwidth
+             (prefill: also counted flop against the measured bf16 peak);
+  cpu_baseline  the port of the reference's fp32 PyTorch recurrence on the host cores, bounded sample.
 
-``--impl reference`` times the reference's CPU implementation of the path (its fp32 PyTorch
-token loop, restated in oracle/wkv7_oracle.py: its package refuses to import on capability
-10.x and its CPU path is that loop) on the same workload.
+``--impl reference`` times the reference's CPU implementation of the path (its fp32 PyTorch token loop, restated
+in oracle/wkv7_oracle.py: its package refuses to import on capability 10.x and its CPU path is that loop) on the
+same workload.  That process hides the GPUs before torch is imported, so the product's libraries are never loaded
+into it.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -36,20 +47,24 @@ import tempfile
 import time
 from pathlib import Path
 
-import torch
-
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+METRIC = "WKV7 tokens/s & % roofline (decode HBM, prefill TC) at 1/2/4/8 B200"
 ALGO_BYTES_DECODE_PAIR = 16384 + 16384 + 6 * 128 + 128  # state in + out, six bf16 rows, one bf16 y row
-ALGO_FLOP_PREFILL_TOKEN_HEAD = 98304  # 12 GEMMs of 64^3 per 64-row chunk
+ALGO_FLOP_PREFILL_TOKEN_HEAD = 98304  # 12 GEMMs of 64^3 per 64 rows
 ALGO_BYTES_PREFILL_TOKEN_HEAD = 7 * 128
 ALGO_BYTES_PREFILL_PAIR = 32768
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel at the headline
-# workload (N=256, H=32), from the ncu capture summarised in profiles/decode_c1_wkv7_recurrent_stream_kernel.md.
-# It is below the algorithmic bytes because part of the written state is still dirty in L2 when the kernel ends.
-DECODE_TRAFFIC_BYTES = 140538368 + 77164544
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per unit of work, from ncu captures of a small case
+# of the same kernel (traffic grows in proportion to the units): decode per (sequence, head), prefill per
+# (token, head).  Decode reads equal the algorithmic bytes; part of the written state is still dirty in L2 when
+# the kernel ends, so the write count is below the 16,512 bytes a pair writes.
+DECODE_TRAFFIC_PER_PAIR = (140538368 + 77164544) / 8192
+PREFILL_TRAFFIC_PER_TOKEN_HEAD = (810.2e6 + 125.6e6) / (32768 * 32)
+MIN_REGION_S = 0.5
+
+DECODE_WORKLOADS = ("c1", "c4_decode")
 
 
 def load_peaks():
@@ -57,6 +72,23 @@ def load_peaks():
     if path.exists():
         return json.loads(path.read_text()), "measured"
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def workload_config(name: str, world: int) -> dict:
+    """The ``config`` object: identical in both arms for the same command line."""
+    from flashrwkv2_b200.workloads import describe
+
+    parts = {"c4": ["c4_decode", "c4_prefill"]}.get(name, [name])
+    return {
+        "workload": " + ".join(describe(p) for p in parts),
+        "headline": describe(parts[0]),
+        "sharding": (f"by sequence over {world} GPU(s), longest first, every shard a slice of the one seeded batch; "
+                     "no collective"),
+        "decay_mode": "retention", "io_dtype": "bf16", "state_dtype": "fp32",
+        "l2": ("decode: state pools in rotation, at least 1 GiB per GPU and every launch's own state larger than "
+               "L2; prefill: inputs of one step larger than L2"),
+        "timed_region": f"K steps x R repeats back to back, R such that the region lasts >= {MIN_REGION_S} s",
+    }
 
 
 class ClockSampler:
@@ -78,6 +110,7 @@ class ClockSampler:
                  "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+        return self
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -107,19 +140,20 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # "under load": the samples in the upper half of the power readings
-        cut = statistics.median(power)
+        cut = statistics.median(power)  # "under load": the samples in the upper half of the power readings
         loaded = [s for s, p in zip(sm, power) if p >= cut] or sm
         return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons),
                 "samples": len(sm), "power_w_max": max(power)}
 
 
-def _event_time_ms(fn, steps, finish=None):
+def _event_time_ms(fn, count, finish=None):
+    import torch
+
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     start.record()
-    for i in range(steps):
+    for i in range(count):
         fn(i)
     if finish is not None:
         finish()
@@ -128,120 +162,132 @@ def _event_time_ms(fn, steps, finish=None):
     return start.elapsed_time(end)
 
 
-def _decode_sets(wl_name, n_sets, rank, world, device, n_seq=None, heads=None):
-    """Rotating input/state sets whose total footprint exceeds L2 several times over."""
-    from flashrwkv2_b200.workloads import make_workload
+def _timed_region(step, steps, warmup, fdist):
+    """Warm up, pick the repeat count from the warm-up, time steps x repeats; returns (ms per step, repeats)."""
+    import torch
 
-    sets = []
-    for i in range(n_sets):
-        wl = make_workload(wl_name, device=device, n_seq=n_seq, heads=heads)
-        if i:  # distinct data per set without re-seeding cost: perturb cheaply
-            for name in "rkv":
-                wl.tensors[name] = wl.tensors[name].roll(i, 0)
-        sets.append(wl)
-    return sets
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    probe = max(3, min(warmup, 10))
+    estimate_ms = fdist.reduce_max(_event_time_ms(step, probe) / probe)
+    repeats = max(1, math.ceil(MIN_REGION_S * 1e3 / max(estimate_ms * steps, 1e-6)))
+    repeats = int(fdist.reduce_max(repeats))
+    fdist.barrier()
+    elapsed_ms = _event_time_ms(step, steps * repeats)
+    fdist.barrier()
+    return fdist.reduce_max(elapsed_ms) / (steps * repeats), repeats
 
 
-def run_ours(args, rank, local_rank, world):
+def _roofline(name, kind, peaks, peak_kind, ms_per_step, pairs, token_heads):
+    if kind == "decode":
+        algo = pairs * ALGO_BYTES_DECODE_PAIR
+        traffic = int(pairs * DECODE_TRAFFIC_PER_PAIR)
+        kernel = "wkv7_recurrent_stream_kernel"
+    else:
+        algo = token_heads * ALGO_BYTES_PREFILL_TOKEN_HEAD + pairs * ALGO_BYTES_PREFILL_PAIR
+        traffic = int(token_heads * PREFILL_TRAFFIC_PER_TOKEN_HEAD)
+        kernel = "wkv7_chunk32_tc_kernel"
+    achieved = algo / (ms_per_step * 1e-3) / 1e9
+    out = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+           "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": traffic, "peak_kind": f"of {peak_kind}",
+           "algorithmic_bytes_per_launch": algo, "kernel": kernel, "per": "launch on the slowest rank's GPU"}
+    if kind != "decode":
+        tflops = token_heads * ALGO_FLOP_PREFILL_TOKEN_HEAD / (ms_per_step * 1e-3) / 1e12
+        out["tensor_tflops"] = round(tflops, 2)
+        out["tensor_frac_of_bf16_peak"] = round(tflops / peaks["bf16_tflops"], 4)
+    return out
+
+
+def measure(name, args, rank, local_rank, world, *, with_e2e=True, steps=None, warmup=None):
+    """One workload on this rank's shard: device-resident timing, roofline, clocks and (optionally) end to end."""
+    import torch
+
     from flashrwkv2_b200 import _lib, dist as fdist
     from flashrwkv2_b200.tmix import wkv7 as ops
     from flashrwkv2_b200.workloads import describe, make_workload
 
     device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
     lib = _lib.load()
     peaks, peak_kind = load_peaks()
-    name = args.workload
-    is_decode = name in ("c1", "c4_decode")
-    sampler = ClockSampler(local_rank)
-
-    per_rank_n = None
-    if name == "c4_decode":
-        per_rank_n = 2048 // world if args.scaling == "strong" else 2048
-    wl0 = make_workload(name, with_tensors=False, n_seq=per_rank_n)
-    heads = wl0.heads
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
+    is_decode = name in DECODE_WORKLOADS
     stream = torch.cuda.current_stream().cuda_stream
+    wl = make_workload(name, device=device, rank=rank, world=world)
+    t = wl.tensors
+    n_seq, heads, tokens = wl.n_seq, wl.heads, wl.total_tokens
+    sampler = ClockSampler(local_rank).start()
 
     if is_decode:
-        n_seq = wl0.n_seq
+        # rotating state pools: every launch streams its state from HBM (no pool is still in L2 when it comes round)
         state_bytes = n_seq * heads * 16384
-        n_sets = max(2, min(8, int(2 * 2**30 // state_bytes)))  # >= 1 GiB of state in rotation when it fits
-        if state_bytes * n_sets < 3 * 126e6:
-            n_sets = int(3 * 126e6 // state_bytes) + 1
-        sets = _decode_sets(name, n_sets, rank, world, device, n_seq=per_rank_n)
-        ys = [torch.empty_like(s.tensors["v"]) for s in sets]
-        tokens_per_step = wl0.total_tokens
+        n_sets = max(2, math.ceil(2**30 / state_bytes))
+        if state_bytes >= 2**30:
+            n_sets = 1
+        pools = [t["state_pool"]] + [t["state_pool"].clone() for _ in range(n_sets - 1)]
+        ys = [torch.empty_like(t["v"]) for _ in range(n_sets)]
 
         def step(i):
-            t = sets[i % n_sets].tensors
+            j = i % n_sets
             rc = lib.frwkv_sm100_wkv7_recurrent(
-                t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, t["state_pool"].data_ptr(),
+                t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, pools[j].data_ptr(),
                 t["r"].data_ptr(), t["w"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), t["a"].data_ptr(),
-                t["b"].data_ptr(), 0, ys[i % n_sets].data_ptr(), 0, n_seq, tokens_per_step, heads, _lib.IO_BF16,
+                t["b"].data_ptr(), 0, ys[j].data_ptr(), 0, n_seq, tokens, heads, _lib.IO_BF16,
                 _lib.DECAY_RETENTION, 1.0, 1, stream)
             if rc:
                 raise RuntimeError(_lib.last_error())
 
-        algo_bytes = n_seq * heads * ALGO_BYTES_DECODE_PAIR
-        l2_note = f"rotating {n_sets} state pools ({state_bytes * n_sets / 2**20:.0f} MiB) > L2"
+        launches_per_step = 1
+        l2_note = f"{n_sets} state pool(s) of {state_bytes / 2**20:.0f} MiB in rotation"
     else:
-        sets = [make_workload(name, device=device, rank=rank if args.scaling == "strong" else 0,
-                              world=world if args.scaling == "strong" else 1)]
-        t = sets[0].tensors
-        wl0 = sets[0]
-        tokens_per_step = wl0.total_tokens
-        n_seq = wl0.n_seq
         y = torch.empty_like(t["v"])
-        pristine = t["state_pool"].clone()
-        need = lib.frwkv_sm100_wkv7_prefill_workspace_bytes(n_seq, tokens_per_step, heads)
+        need = lib.frwkv_sm100_wkv7_prefill_workspace_bytes(n_seq, tokens, heads)
         ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
         err = torch.zeros(1, dtype=torch.int32, device=device)
-        max_len = max(wl0.lengths)
+        max_len = max(wl.lengths)
 
         def step(i):
             rc = lib.frwkv_sm100_wkv7_prefill(
                 t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, t["state_pool"].data_ptr(),
                 t["r"].data_ptr(), t["w"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), t["a"].data_ptr(),
-                t["b"].data_ptr(), 0, y.data_ptr(), 0, n_seq, tokens_per_step, heads, _lib.IO_BF16,
+                t["b"].data_ptr(), 0, y.data_ptr(), 0, n_seq, tokens, heads, _lib.IO_BF16,
                 _lib.DECAY_RETENTION, 1.0, max_len, _lib.PREFILL_AUTO, ws.data_ptr(), need, err.data_ptr(), stream)
             if rc:
                 raise RuntimeError(_lib.last_error())
 
-        algo_bytes = tokens_per_step * heads * ALGO_BYTES_PREFILL_TOKEN_HEAD + n_seq * heads * ALGO_BYTES_PREFILL_PAIR
-        l2_note = f"inputs {tokens_per_step * heads * 896 / 2**20:.0f} MiB per step > L2"
+        # length ranking (2..2048 sequences), recurrence kernel for rows under 16 tokens, chunk kernel
+        launches_per_step = 3 if 1 < n_seq <= 2048 else 2
+        l2_note = f"inputs of one step {tokens * heads * 896 / 2**20:.0f} MiB"
 
-    # ---- device-resident timing -------------------------------------------------------
-    sampler.start()
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    fdist.barrier()
-    elapsed_ms = _event_time_ms(step, args.steps)
-    fdist.barrier()
-    elapsed_ms = fdist.reduce_max(elapsed_ms)
-    total_tokens = fdist.reduce_sum(tokens_per_step)
-    ms_per_step = elapsed_ms / args.steps
-    value = total_tokens / (ms_per_step * 1e-3)
-    # decode: one kernel per step; prefill (auto): length ranking (2..2048 sequences), recurrence for short rows, chunk kernel
-    launches = args.steps * (1 if is_decode else (3 if 1 < n_seq <= 2048 else 2))
+    ms_per_step, repeats = _timed_region(step, steps, warmup, fdist)
+    total_tokens = fdist.reduce_sum(tokens)
+    clocks = sampler.stop()
+    max_pairs = int(fdist.reduce_max(n_seq * heads))
+    max_token_heads = int(fdist.reduce_max(tokens * heads))
+    block = {
+        "workload": describe(name), "value": round(total_tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
+        "ms_per_step": round(ms_per_step, 6), "steps": steps, "repeats": repeats,
+        "tokens_per_step": int(total_tokens), "l2": l2_note,
+        "gpu_launches": steps * repeats * launches_per_step,
+        "roofline": _roofline(name, "decode" if is_decode else "prefill", peaks, peak_kind, ms_per_step, max_pairs,
+                              max_token_heads),
+        "clocks": clocks,
+    }
+    if not is_decode:
+        block["error_flag"] = int(err.item())
 
-    # ---- end to end through the public operator, host buffers ---------------------------
-    src = sets[0].tensors
-    h2d = sum(src[n].numel() * src[n].element_size() for n in "rwkvab")
-    d2h = src["v"].numel() * src["v"].element_size()
-    e2e = None
-    if args.no_e2e or h2d > 8 * 2**30:  # bound pinned host memory on shared boxes
-        clocks = sampler.stop()
-    else:
+    h2d = sum(t[n].numel() * t[n].element_size() for n in "rwkvab")
+    d2h = t["v"].numel() * t["v"].element_size()
+    if with_e2e and not args.no_e2e and h2d <= 8 * 2**30:  # bound pinned host memory on shared boxes
         # the caller's six token tensors live in one pinned host block -> one host->device copy per step.
         # Two streams, as a serving loop would run it: step i+1's upload overlaps step i's kernel and the
         # download of its y (PCIe is full duplex); every step still uploads its inputs and downloads its result.
-        host = torch.stack([src[n].cpu() for n in "rwkvab"]).pin_memory()
+        host = torch.stack([t[n].cpu() for n in "rwkvab"]).pin_memory()
         dev_in = [torch.empty_like(host, device=device) for _ in range(2)]
-        y_host = [torch.empty(src["v"].shape, dtype=src["v"].dtype).pin_memory() for _ in range(2)]
-        pool = src["state_pool"]
-        cu, slots = src["cu_seqlens"], src["state_indices"]
-        ticket = ops.prepare_tmix_wkv7_recurrent_metadata(cu, slots, total_tokens=tokens_per_step,
+        y_host = [torch.empty(t["v"].shape, dtype=t["v"].dtype).pin_memory() for _ in range(2)]
+        pool, cu, slots = t["state_pool"], t["cu_seqlens"], t["state_indices"]
+        ticket = ops.prepare_tmix_wkv7_recurrent_metadata(cu, slots, total_tokens=tokens,
                                                           state_pool_size=pool.shape[0])
         op = (ops.infer_tmix_wkv7_recurrent_fp32io16_forward_varlen if is_decode
               else ops.infer_tmix_wkv7_prefill_fp32io16_forward_varlen)
@@ -251,6 +297,7 @@ def run_ours(args, rank, local_rank, world):
         consumed = [torch.cuda.Event(), torch.cuda.Event()]
         for ev in consumed:
             ev.record(main_stream)
+        host_s = [0.0, 0]
 
         def e2e_step(i):
             j = i % 2
@@ -260,104 +307,84 @@ def run_ours(args, rank, local_rank, world):
                 uploaded[j].record(up_stream)
             main_stream.wait_event(uploaded[j])
             d = dev_in[j]
+            begin = time.perf_counter()
             out = op(d[0], d[1], d[2], d[3], d[4], d[5], state_pool=pool, cu_seqlens=cu, state_indices=slots,
                      validated_metadata=ticket, decay_mode="retention")
+            host_s[0] += time.perf_counter() - begin
+            host_s[1] += 1
             consumed[j].record(main_stream)
             y_host[j].copy_(out, non_blocking=True)
 
         def e2e_finish():
             main_stream.wait_stream(up_stream)
 
-        e2e_steps = max(3, min(args.steps, 2000 if is_decode else 20))
-        for i in range(min(args.warmup, 10)):
+        for i in range(5):
             e2e_step(i)
         torch.cuda.synchronize()
+        probe_ms = fdist.reduce_max(_event_time_ms(e2e_step, 5, e2e_finish) / 5)
+        e2e_steps = int(fdist.reduce_max(max(2000 if probe_ms < 0.25 else 3, math.ceil(MIN_REGION_S * 1e3 / probe_ms))))
+        host_s[0], host_s[1] = 0.0, 0
         fdist.barrier()
         e2e_ms = _event_time_ms(e2e_step, e2e_steps, e2e_finish)
         fdist.barrier()
         e2e_ms = fdist.reduce_max(e2e_ms)
-        clocks = sampler.stop()
-        e2e = {"value": round(total_tokens / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+        block["e2e"] = {"value": round(total_tokens / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "tokens/s",
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                        "ms_per_step": round(e2e_ms / e2e_steps, 6),
+                        "host_us_per_operator_call": round(host_s[0] / max(1, host_s[1]) * 1e6, 2)}
+    else:
+        block["e2e"] = None
+    block["_workload_object"] = wl
+    return block
 
-    achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": DECODE_TRAFFIC_BYTES if name == "c1" else None,
-                "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo_bytes,
-                "kernel": "wkv7_recurrent_stream_kernel" if is_decode else "wkv7 prefill"}
-    if not is_decode:
-        flops = tokens_per_step * heads * ALGO_FLOP_PREFILL_TOKEN_HEAD
-        roofline["tensor_tflops"] = round(flops / (ms_per_step * 1e-3) / 1e12, 2)
-        roofline["tensor_frac_of_bf16_peak"] = round(roofline["tensor_tflops"] / peaks["bf16_tflops"], 4)
 
+def run_ours(args, rank, local_rank, world):
+    import torch
+
+    torch.cuda.set_device(local_rank)
+    name = args.workload
+    head_name = "c4_decode" if name == "c4" else name
+    head = measure(head_name, args, rank, local_rank, world)
+    wl = head.pop("_workload_object")
     line = {
-        "metric": "WKV7 tokens/s & % roofline (decode HBM, prefill TC) at 1/2/4/8 B200",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 6), "higher_is_better": True, "scaling": args.scaling,
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": describe(name) + (f"; {n_seq} sequences per GPU" if world > 1 else ""),
-                   "tokens_per_step_per_gpu": tokens_per_step, "l2": l2_note, "decay_mode": "retention",
-                   "io_dtype": "bf16", "state_dtype": "fp32"},
-        "clocks": clocks,
-        "e2e": e2e,
-        "gpu_launches": launches,
-        "roofline": roofline,
+        "metric": METRIC, "value": head["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(name, world),
+        "repeats": head["repeats"], "tokens_per_step": head["tokens_per_step"], "clocks": head["clocks"],
+        "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "roofline": head["roofline"],
     }
-
     if rank == 0 and world == 1 and not args.no_extras:
-        line["cpu_baseline"] = cpu_baseline(name, sets[0])
-        if is_decode:
+        line["cpu_baseline"] = cpu_baseline(head_name, wl)
+    del wl
+    torch.cuda.empty_cache()
+    if name == "c4":
+        prefill = measure("c4_prefill", args, rank, local_rank, world, with_e2e=False)
+        prefill.pop("_workload_object")
+        line["prefill"] = prefill
+        line["gpu_launches"] += prefill["gpu_launches"]
+        torch.cuda.empty_cache()
+    if world == 1 and not args.no_extras and name == "c4":
+        extras = {}
+        for extra in ("c1", "c2", "c3"):
             try:
-                line["prefill"] = prefill_extra(lib, _lib, device, peaks, stream)
+                block = measure(extra, args, rank, local_rank, world, with_e2e=extra == "c1")
+                block.pop("_workload_object")
+                extras[extra] = block
             except RuntimeError as error:  # reported, not hidden
-                line["prefill"] = {"error": str(error)}
-            try:
-                line["gpu_baseline"] = gpu_baseline(device, sets)
-            except Exception as error:  # a baseline that cannot load or run must not take the bench line with it
-                line["gpu_baseline"] = {"error": f"{type(error).__name__}: {error}"}
-    return line
-
-
-def prefill_extra(lib, _lib, device, peaks, stream):
-    """Dense prefill (8 x 4096 tokens, H=32) timed in the same run: tokens/s, HBM and tensor fractions."""
-    from flashrwkv2_b200.workloads import make_workload
-
-    wl = make_workload("c2", device=device)
-    t = wl.tensors
-    n_seq, heads, total = wl.n_seq, wl.heads, wl.total_tokens
-    y = torch.empty_like(t["v"])
-    need = lib.frwkv_sm100_wkv7_prefill_workspace_bytes(n_seq, total, heads)
-    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
-    err = torch.zeros(1, dtype=torch.int32, device=device)
-    out = {}
-    for label, strategy in (("auto", _lib.PREFILL_AUTO), ("recurrent", _lib.PREFILL_RECURRENT)):
-        def step(i):
-            rc = lib.frwkv_sm100_wkv7_prefill(
-                t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, t["state_pool"].data_ptr(),
-                t["r"].data_ptr(), t["w"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), t["a"].data_ptr(),
-                t["b"].data_ptr(), 0, y.data_ptr(), 0, n_seq, total, heads, _lib.IO_BF16, _lib.DECAY_RETENTION,
-                1.0, 4096, strategy, ws.data_ptr(), need, err.data_ptr(), stream)
-            if rc:
-                raise RuntimeError(_lib.last_error())
+                extras[extra] = {"error": str(error)}
+            torch.cuda.empty_cache()
         try:
-            for i in range(3):
-                step(i)
-            ms = _event_time_ms(step, 10) / 10
-        except RuntimeError as error:
-            out[label] = {"error": str(error)}
-            continue
-        algo = total * heads * ALGO_BYTES_PREFILL_TOKEN_HEAD + n_seq * heads * ALGO_BYTES_PREFILL_PAIR
-        flops = total * heads * ALGO_FLOP_PREFILL_TOKEN_HEAD
-        out[label] = {"tokens_per_s": round(total / (ms * 1e-3), 1), "ms_per_step": round(ms, 4),
-                      "hbm_frac": round(algo / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                      "tensor_frac_of_bf16_peak": round(flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4),
-                      "error_flag": int(err.item())}
-    out["workload"] = "c2: prefill N=8 T=4096 H=32 D=64 bf16"
-    return out
+            extras["gpu_baseline"] = gpu_baseline(torch.device("cuda", local_rank))
+        except Exception as error:  # a baseline that cannot load or run must not take the bench line with it
+            extras["gpu_baseline"] = {"error": f"{type(error).__name__}: {error}"}
+        line["extras"] = extras
+    return line
 
 
 def _cpu_sample(name, wl, limit_s=10.0, use_c=False):
     """Time the CPU recurrence on a bounded sample of the workload; returns (tokens/s, cores, text)."""
+    import torch
+
     from oracle import c_oracle
     from oracle.wkv7_oracle import wkv7_oracle
 
@@ -399,13 +426,16 @@ def cpu_baseline(name, wl):
             "c_openmp_port": {"value": round(c_value, 1), "cores": c_cores}, "host_cpus": os.cpu_count()}
 
 
-def gpu_baseline(device, decode_sets):
+def gpu_baseline(device):
     """The reference project's own CUDA kernels on this GPU (a baseline, like cpu_baseline): its unmodified
-    recurrent and rl_infctx chunk-forward sources built for sm_100 into oracle/_ref (oracle/build_ref.py), called
-    through the reference's native symbols.  Decode: the headline workload, ticket prepared once, rotating sets.
-    Prefill: the dense 8 x 4096 workload through the recurrent operator (what the reference's inference path runs
-    for T > 1) and through the rl_infctx chunk operator (chunk 64; clones and workspaces included, as its API does).
-    The reference has only the logits decay mode; kernel time does not depend on the values."""
+    recurrent and rl_infctx chunk-forward sources built for sm_100 (oracle/build_ref.py), called through the
+    reference's native symbols.  Decode: 256 x H32, ticket prepared once, rotating state pools.  Prefill: the dense
+    8 x 4096 workload through the recurrent operator (what the reference's inference path runs for T > 1) and
+    through the rl_infctx chunk operator (chunk 64; clones and workspaces included, as its API does).  The
+    reference has only the logits decay mode; kernel time does not depend on the values.  A missing build is
+    reported here, in the bench line, not skipped silently."""
+    import torch
+
     from flashrwkv2_b200.workloads import make_workload
     from oracle.build_ref import load_ref
 
@@ -414,28 +444,24 @@ def gpu_baseline(device, decode_sets):
         return {"unavailable": "oracle/_ref/_C_ref.so not built (needs a reference checkout at build time)"}
     out = {"kind": "reference kernels, unmodified sources compiled for sm_100"}
     names = ("r", "w", "k", "v", "a", "b")
-    # decode
-    tickets, ys = [], []
-    for wl in decode_sets:
-        t = wl.tensors
-        tickets.append(ref.prepare_tmix_wkv7_recurrent_metadata(t["cu_seqlens"], t["state_indices"], wl.total_tokens,
-                                                                 t["state_pool"].shape[0], 1))
-        ys.append(torch.empty_like(t["v"]))
+    wl = make_workload("c1", device=device)
+    t = wl.tensors
+    pools = [t["state_pool"]] + [t["state_pool"].clone() for _ in range(7)]
+    ticket = ref.prepare_tmix_wkv7_recurrent_metadata(t["cu_seqlens"], t["state_indices"], wl.total_tokens,
+                                                      t["state_pool"].shape[0], 1)
+    y = torch.empty_like(t["v"])
 
     def decode_step(i):
-        j = i % len(decode_sets)
-        t = decode_sets[j].tensors
-        ref.tmix_wkv7_recurrent_fp32_from_decay_logits(t["cu_seqlens"], t["state_indices"], t["state_pool"],
-                                                       *(t[n] for n in names), ys[j], 1.0, None, tickets[j], 1)
+        ref.tmix_wkv7_recurrent_fp32_from_decay_logits(t["cu_seqlens"], t["state_indices"], pools[i % 8],
+                                                       *(t[n] for n in names), y, 1.0, None, ticket, 1)
 
     for i in range(5):
         decode_step(i)
     steps = 200
     ms = _event_time_ms(decode_step, steps) / steps
-    tokens = decode_sets[0].total_tokens
-    out["decode"] = {"kernel": "wkv_fp32_v2_small_warp_kernel", "tokens_per_s": round(tokens / (ms * 1e-3), 1),
-                     "us_per_step": round(ms * 1e3, 2)}
-    # prefill
+    out["decode"] = {"workload": "c1", "kernel": "wkv_fp32_v2_small_warp_kernel",
+                     "tokens_per_s": round(wl.total_tokens / (ms * 1e-3), 1), "us_per_step": round(ms * 1e3, 2)}
+    del pools
     wl = make_workload("c2", device=device)
     t = wl.tensors
     y = torch.empty_like(t["v"])
@@ -455,7 +481,7 @@ def gpu_baseline(device, decode_sets):
                                                            1.0, None)
         return step
 
-    out["prefill"] = {"workload": "c2: prefill N=8 T=4096 H=32 D=64 bf16"}
+    out["prefill"] = {"workload": "c2"}
     for label, fn in (("recurrent (wkv_fp32_v2_kernel)", recurrent_step),
                       ("rl_infctx chunk 64, recompute", chunk_step(1)),
                       ("rl_infctx chunk 64, materialized", chunk_step(0))):
@@ -468,20 +494,21 @@ def gpu_baseline(device, decode_sets):
 
 def run_reference(args, rank, world):
     """The reference's CPU implementation of the path on the host cores (rank 0 only)."""
-    from flashrwkv2_b200.workloads import describe, make_workload
+    import torch
+
+    from flashrwkv2_b200.workloads import make_workload
 
     if rank != 0:
         return None
     # torchrun pins OMP_NUM_THREADS=1; the CPU path gets every host thread it can use
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    name = args.workload
-    per_rank_n = 2048 if name == "c4_decode" else None
-    wl = make_workload(name, n_seq=per_rank_n) if name in ("c1", "c4_decode") else make_workload(
-        name, n_seq=8 if name != "c3" else None, seq_len=256)
-    steps_ms = []
+    name = "c4_decode" if args.workload == "c4" else args.workload
+    if name in DECODE_WORKLOADS:
+        wl = make_workload(name)
+    else:  # a prefix of every sequence is what a step times: generate no more than that
+        wl = make_workload(name, n_seq=8 if name != "c3" else None, seq_len=256)
     per_step_limit = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
-    sample = ""
-    values = []
+    sample, values, steps_ms = "", [], []
     for i in range(args.warmup + args.steps):
         begin = time.perf_counter()
         value, cores, sample = _cpu_sample(name, wl, limit_s=per_step_limit, use_c=False)
@@ -490,18 +517,16 @@ def run_reference(args, rank, world):
             steps_ms.append((time.perf_counter() - begin) * 1e3)
     value = statistics.mean(values)
     return {
-        "impl": "reference",
-        "metric": "WKV7 tokens/s & % roofline (decode HBM, prefill TC) at 1/2/4/8 B200",
+        "impl": "reference", "metric": METRIC,
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(statistics.mean(steps_ms), 3), "higher_is_better": True, "scaling": args.scaling,
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": describe(name), "decay_mode": "retention", "io_dtype": "bf16", "state_dtype": "fp32"},
+        "ms_per_step": round(statistics.mean(steps_ms), 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.workload, world),
         "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": "each step: " + sample},
         "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": ("the reference ships no sm_100 kernel and its import rejects capability 10.x; its CPU "
                  "implementation of this path is the fp32 PyTorch token loop of its test-suite, restated in "
-                 "oracle/wkv7_oracle.py"),
+                 "oracle/wkv7_oracle.py; the GPUs are hidden from this process"),
     }
 
 
@@ -511,18 +536,21 @@ def main():
     parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    parser.add_argument("--workload", default="c1", choices=("c1", "c2", "c3", "c4_decode", "c4_prefill"))
-    parser.add_argument("--scaling", default="weak", choices=("weak", "strong"))
+    parser.add_argument("--workload", default="c4", choices=("c4", "c1", "c2", "c3", "c4_decode", "c4_prefill"))
     parser.add_argument("--no-extras", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     args = parser.parse_args()
-    decode = args.workload in ("c1", "c4_decode")
     if args.impl == "reference":
+        # the reference arm is CPU code: hide the GPUs before torch (and the package) are imported, so that
+        # none of the product's shared libraries is loaded into this process
+        os.environ["CUDA_VISIBLE_DEVICES"] = ""
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup
     else:
-        args.steps = (20000 if decode else 20) if args.steps is None else args.steps
-        args.warmup = (200 if decode else 3) if args.warmup is None else max(3, args.warmup)
+        args.steps = 20 if args.steps is None else args.steps
+        args.warmup = 5 if args.warmup is None else max(3, args.warmup)
+
+    import torch
 
     from flashrwkv2_b200 import dist as fdist
 

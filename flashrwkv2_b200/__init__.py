@@ -2,7 +2,7 @@
 
 Backend selection mirrors rwkv-rs/FlashRWKV2 flashrwkv2/__init__.py:12-55: the private
 native module is chosen by compute capability and published as ``flashrwkv2_b200._C``.
-The only backend is ``_C_sm100`` (capability 10.x); there is no Triton/TileLang path,
+The only backend is ``_C_sm100`` (capability 10.0 exactly: an sm_100a cubin); there is no Triton/TileLang path,
 no multi-backend dispatch and no CPU fallback.
 """
 
@@ -18,8 +18,9 @@ _NATIVE_BACKENDS = (
 
 def _backend_module_name(capability: tuple[int, int]) -> str:
     major, minor = capability
-    matches = [(target, name) for target, name in _NATIVE_BACKENDS
-               if target[0] == major and target[1] <= minor]
+    # the backend is an sm_100a cubin ("a" = architecture-specific features: tcgen05, TMEM): it runs on
+    # capability 10.0 exactly, not on later 10.x parts
+    matches = [(target, name) for target, name in _NATIVE_BACKENDS if target == (major, minor)]
     if not matches:
         have = ", ".join(f"sm{t[0]}{t[1]}" for t, _ in _NATIVE_BACKENDS)
         raise RuntimeError(

@@ -42,7 +42,15 @@ def load() -> ctypes.CDLL:
         raise NativeLibraryMissing(
             f"{LIB_PATH} is not built; run `python -m flashrwkv2_b200.build` "
             "(there is no CPU or PyTorch fallback for the WKV7 operator)")
-    lib = ctypes.CDLL(str(LIB_PATH))
+    lib = declare(ctypes.CDLL(str(LIB_PATH)))
+    if lib.frwkv_sm100_abi_version() != ABI_VERSION:
+        raise RuntimeError("libfrwkv_sm100.so ABI version mismatch; rebuild it")
+    _lib = lib
+    return lib
+
+
+def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
+    """Attach the argument and result types of every entry point include/frwkv_sm100.h declares."""
     vp, ci, cf, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
     lib.frwkv_sm100_abi_version.restype = ci
     lib.frwkv_sm100_abi_version.argtypes = []
@@ -58,9 +66,6 @@ def load() -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_prefill.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     lib.frwkv_sm100_wkv7_prefill_workspace_bytes.restype = sz
     lib.frwkv_sm100_wkv7_prefill_workspace_bytes.argtypes = [ci, ci, ci]
-    if lib.frwkv_sm100_abi_version() != ABI_VERSION:
-        raise RuntimeError("libfrwkv_sm100.so ABI version mismatch; rebuild it")
-    _lib = lib
     return lib
 
 

@@ -98,24 +98,41 @@ def _digest(src: Path) -> str:
     return h.hexdigest()[:16]
 
 
-def _compile(src: Path, verbose: bool) -> Path:
-    obj = OBJ_DIR / (src.stem + "." + _digest(src) + ".o")
+def _compile(src: Path, verbose: bool, extra: tuple[str, ...] = (), tag: str = "") -> Path:
+    stem = src.stem + tag
+    obj = OBJ_DIR / (stem + "." + _digest(src) + ".o")
     if obj.exists():
         return obj
-    for stale in OBJ_DIR.glob(src.stem + ".*.o"):
+    for stale in OBJ_DIR.glob(stem + ".*.o"):
         stale.unlink()
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
     env = dict(os.environ)
     env.pop("CC", None)
     env.pop("CXX", None)
     res = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    log = OBJ_DIR / (src.stem + ".ptxas.txt")
+    log = OBJ_DIR / (stem + ".ptxas.txt")
     log.write_text(res.stderr)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{res.stderr}")
     if verbose:
         print(res.stderr, file=sys.stderr)
     return obj
+
+
+def _link(lib: Path, objs: list[Path], stamp: Path, force: bool) -> Path:
+    wanted = "\n".join(o.name for o in objs)
+    if lib.exists() and stamp.exists() and stamp.read_text() == wanted and not force:
+        return lib
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
+           "-Xcompiler", "-fPIC"]
+    res = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stderr}")
+    stamp.write_text(wanted)
+    return lib
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
@@ -127,23 +144,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     srcs = sources()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
-    stamp = LIB_DIR / ".objects"
-    wanted = "\n".join(o.name for o in objs)
-    if LIB.exists() and stamp.exists() and stamp.read_text() == wanted and not force:
-        return LIB
-    env = dict(os.environ)
-    env.pop("CC", None)
-    env.pop("CXX", None)
-    cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
-           "-Xcompiler", "-fPIC"]
-    res = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    if res.returncode != 0:
-        raise RuntimeError(f"link failed:\n{res.stderr}")
-    stamp.write_text(wanted)
-    return LIB
+    return _link(LIB, objs, LIB_DIR / ".objects", force)
+
+
+# The same sources compiled with -DFRWKV_TEST_HOOKS: a second library that only the tests load.  It adds
+# frwkv_sm100_test_skip_commit() and frwkv_sm100_test_recurrent_parts(); the product library has neither.
+TEST_LIB = PKG.parent / "tests" / "lib" / "libfrwkv_sm100_testhooks.so"
+
+
+def build_testhooks(force: bool = False) -> Path:
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    TEST_LIB.parent.mkdir(parents=True, exist_ok=True)
+    srcs = sources()
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, False, ("-DFRWKV_TEST_HOOKS",), ".hooks"), srcs))
+    return _link(TEST_LIB, objs, TEST_LIB.parent / ".objects", force)
 
 
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
     print(build_extension(force="--force" in sys.argv))
+    print(build_testhooks(force="--force" in sys.argv))

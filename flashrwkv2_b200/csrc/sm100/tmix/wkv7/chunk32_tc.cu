@@ -1,21 +1,32 @@
 // WKV7 chunked prefill on tcgen05 tensor cores, 32-row chunks, two CTAs resident per SM.
 //
-// Same algebra, precision scheme and data movement as the 64-row kernel in chunk_tc.cu (see the
-// header there); what changes is the footprint.  With 32-row chunks the stacked operands
-// [At; Rt], [Bt; Kt], [A_ak; A_rk] and [T; A_rb] have 64 rows, so every product is a natural
-// M=64 MMA (no padding rows), one CTA needs 112 KB of shared memory and 256 TMEM columns, and
-// two CTAs of 288 threads (96 registers) share an SM: while one waits for its MMAs or a
-// barrier the other one's CUDA-core phases run.  A 64-row accumulator of an M=64 MMA puts row i
-// in TMEM lane 32*(i/16) + i%16, i.e. every warp quadrant holds 16 rows in its lanes 0..15; the
-// read-backs use the 16x256b fragment shape, which spreads those 16 rows over all 32 threads.
-// Eight warps compute; a ninth issues every MMA and TMA load (see the loop below).  Inside the stacked operands the
-// two kinds of rows alternate in groups of eight (token t: 16*(t/8) + t%8 and eight further), so that every
-// thread's fragment holds one row of each kind and all eight warps share every read-back.
+// One CTA walks one (sequence, head) chunk by chunk with the fp32 state resident in TMEM.  With 32-row chunks
+// the stacked operands [At; Rt], [Bt; Kt], [A_ak; A_rk] and [T; A_rb] have 64 rows, so every product is a
+// natural M=64 MMA, one CTA needs about 111 KB of shared memory and 256 TMEM columns, and two CTAs of 288
+// threads (96 registers) share an SM: while one waits for its MMAs or a barrier the other one's CUDA-core
+// phases run.  A 64-row accumulator of an M=64 MMA puts row i in TMEM lane 32*(i/16) + i%16, i.e. every warp
+// quadrant holds 16 rows in its lanes 0..15; the read-backs use the 16x256b fragment shape, which spreads
+// those 16 rows over all 32 threads.  Eight warps compute; a ninth issues every MMA and TMA load.  Inside the
+// stacked operands the two kinds of rows alternate in groups of eight (token t: 16*(t/8) + t%8 and eight
+// further), so that every thread's fragment holds one row of each kind and all eight warps share every
+// read-back.
 //
-// Per chunk of L <= 32 rows (g_t = inclusive cumulative retention inside the chunk):
+// Per chunk of L <= 32 rows (g_t = inclusive product of the retentions inside the chunk, g_L its last value):
+//     At = a g_{t-1}   Rt = r g_t   Bt = b / g_t   Kt = k / g_t   Bl = b g_L / g_t   Kl = k g_L / g_t
 //     P  = [At; Rt] [Bt; Kt]^T  (64x64) -> A_ab, A_ak (strictly lower), A_rb, A_rk (lower), 32x32 each
-//     Q  = [At; Rt] S0 + [A_ak; A_rk] V      (rows 0..31 = W, rows 32..63 = part of Y)
-//     U  = (I - A_ab)^-1 W ;  Y = scale (Q[32..] + A_rb U) ;  S <- diag(g_L)(S0 + Bt^T U + Kt^T V)
+//     Q  = [At; Rt] S0 + [A_ak; A_rk] V      (rows of the At kind = W, rows of the Rt kind = part of Y)
+//     U  = (I - A_ab)^-1 W ;  Y = scale (Q[Rt rows] + A_rb U) ;  S <- diag(g_L) S0 + Bl^T U + Kl^T V
+//
+// Precision.  The 5e-3 gate on max|error|/RMS needs about 13 significant bits in the operands of the
+// products that see the decay-scaled tokens twice (P) and 11 elsewhere; the cost of a product is the number
+// of 16-bit terms it is issued as.  P is the only product whose operands are unbounded (1/g_t reaches 2^28
+// over 32 rows), so it stays in bf16 with three terms (hi*hi + hi*lo + lo*hi, 16 bits).  Every other product
+// uses operands that are bounded by the data (At, Rt, Bl, Kl carry factors <= 1; the masked blocks of P, T,
+// W, U, V and the state are data-sized) and runs in fp16: one term (11 bits) for T W, A_rb U and Bl^T U, two
+// terms for [At; Rt] S0 (hi + lo of the state), [A_ak; A_rk] V and Kl^T V (hi + lo of the left operand; V is
+// exact).  34 MMAs per chunk instead of the 50 of an all-three-term scheme; emulated and measured error
+// 1.1e-3 .. 2.4e-3 on the benchmark distributions, the reference's test distributions and on channels that
+// always decay at the fastest rate.
 #include "chunk_common.cuh"
 
 namespace frwkv {
@@ -35,27 +46,33 @@ constexpr int kChunk = 32;
 
 // ---- shared-memory map (bytes) -------------------------------------------------------------
 constexpr uint32_t kStride64 = 8 * 128 + 16;  // stride between 16-byte chunks of a 64-row tile (padded)
-constexpr uint32_t kTileK64 = 8 * kStride64;  // 64 rows x 64 columns, one bf16 part: 8320
-constexpr uint32_t kTileK32 = 4 * kStride64;  // 64 rows x 32 columns, one bf16 part: 4160
+constexpr uint32_t kTileK64 = 8 * kStride64;  // 64 rows x 64 columns, one 16-bit part: 8320
+constexpr uint32_t kTileK32 = 4 * kStride64;  // 64 rows x 32 columns, one 16-bit part: 4160
 constexpr uint32_t kStride32 = 4 * 128 + 16;  // stride between 16-byte chunks of a 32-row tile (padded)
-constexpr uint32_t kTileV = 8 * kStride32;    // 32 rows x 64 columns, one bf16 part: 4224
+constexpr uint32_t kTile32 = 8 * kStride32;   // 32 rows x 64 columns, one 16-bit part: 4224
 
 constexpr uint32_t kRawTile = kChunk * 128;           // one [32][64] 16-bit tile as TMA writes it
 constexpr uint32_t kOffRaw = 0;                       // r, w, k, v, a, b
-constexpr uint32_t kOffX1 = kOffRaw + 6 * kRawTile;   // [At; Rt] hi, lo (64 x 64)
-constexpr uint32_t kOffX2 = kOffX1 + 2 * kTileK64;    // [Bt; Kt] hi, lo (64 x 64)
-constexpr uint32_t kOffX3 = kOffX2 + 2 * kTileK64;    // [A_ak; A_rk] hi, lo (64 x 32)
-constexpr uint32_t kOffX4 = kOffX3 + 2 * kTileK32;    // [T; A_rb] hi, lo (64 x 32)
-constexpr uint32_t kOffOp = kOffX4 + 2 * kTileK32;    // S0 (64 rows) / W / U (32 rows) operand hi, lo
-constexpr uint32_t kOffV = kOffOp + 2 * kTileK64;     // V operand hi, lo (32 rows x 64)
-constexpr uint32_t kOffMisc = kOffV + 2 * kTileV;     // gamma_L[2][64], group sums [8][64], barriers
-constexpr uint32_t kMiscBytes = 2 * 64 * 4 + kWarps * 64 * 4 + 64;
-// fp32 scratch of the 32x32 inverse.  It has its own area: the staging area must stay free for the next chunk's
-// load, which is issued a whole chunk ahead.  The 16x16 block product of level 1 lives in T's upper-right block,
-// which is zero and never stored.
+constexpr uint32_t kOffX1 = kOffRaw + 6 * kRawTile;   // [At; Rt] bf16 hi, lo (64 x 64): left operand of P
+constexpr uint32_t kOffX2 = kOffX1 + 2 * kTileK64;    // [Bt; Kt] bf16 hi, lo (64 x 64): right operand of P  (*)
+constexpr uint32_t kOffX1h = kOffX2 + 2 * kTileK64;   // [At; Rt] fp16 (64 x 64): left operand of Q
+constexpr uint32_t kOffBl = kOffX1h + kTileK64;       // Bl fp16 (32 rows = tokens, 64 key channels)
+constexpr uint32_t kOffKl = kOffBl + kTile32;         // Kl fp16 hi, lo
+constexpr uint32_t kOffX4 = kOffKl + 2 * kTile32;     // [T; A_rb] fp16 (64 x 32)
+constexpr uint32_t kOffOp = kOffX4 + kTileK32;        // S0 hi, lo (64 rows) / W / U (32 rows, hi only) fp16, right operand
+constexpr uint32_t kOffV = kOffOp + 2 * kTileK64;     // V fp16 (32 rows x 64)
+constexpr uint32_t kOffMisc = kOffV + kTile32;        // group products [8][64], barriers
+constexpr uint32_t kMiscBytes = kWarps * 64 * 4 + 64;
+// (*) The operands of P are written during the previous chunk's last products and are dead as soon as P has
+// completed, which is when the masked blocks of P and the scratch of the inverse come to life (and those are dead
+// again before the next chunk's operands are written): [A_ak; A_rk] and the A_ab scratch share the area of [Bt; Kt].
+constexpr uint32_t kOffX3 = kOffX2;                   // [A_ak; A_rk] fp16 hi, lo (64 x 32)
+// fp32 scratch of the 32x32 inverse.  The 16x16 block product of level 1 lives in T's upper-right block, which is
+// zero and never stored.
 constexpr int kInvLd = 36;
-constexpr uint32_t kOffAb = kOffMisc + kMiscBytes;     // A_ab [32][36]
-constexpr uint32_t kOffTi = kOffAb + 32 * kInvLd * 4;  // T    [32][36]
+constexpr uint32_t kOffAb = kOffX3 + 2 * kTileK32;     // A_ab [32][36]
+static_assert(kOffAb + 32 * kInvLd * 4 <= kOffX1h, "masked blocks and A_ab scratch must fit in the area of [Bt; Kt]");
+constexpr uint32_t kOffTi = kOffMisc + kMiscBytes;     // T    [32][36]
 constexpr int kMbLd = kInvLd;
 constexpr uint32_t kOffMb = kOffTi + 16 * 4;           // block product [16][16] at T[0..15][16..31]
 constexpr uint32_t kSmemBytes = kOffTi + 32 * kInvLd * 4 + 128;
@@ -91,14 +108,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   const int n_chunks = (len + kChunk - 1) / kChunk;
   const int slot = p.slots[seq];
 
-  float* gamma_l = reinterpret_cast<float*>(smem + kOffMisc);
-  float* group_sum = gamma_l + 2 * 64;  // [8][64] log2-decay sums of each 4-row group (gamma_l: [2][64] by chunk parity)
-  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_sum + kWarps * 64);
-  uint64_t* bar_mma = bar_tma + 1;
+  float* group_prod = reinterpret_cast<float*>(smem + kOffMisc);  // [8][64] retention products of each 4-row group
+  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_prod + kWarps * 64);
+  uint64_t* bar_mma = bar_tma + 1;    // Q, U, Y of every chunk, in this order
   uint64_t* bar_state = bar_tma + 2;  // its own barrier: two commits may not complete two phases of one
   uint64_t* bar_drain = bar_tma + 3;  // the issuer warp's last commit: every MMA has retired before TMEM is freed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_drain + 1);
+  uint64_t* bar_p = bar_tma + 4;      // P of the next chunk is issued while this chunk's Y is still outstanding
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 5);
   volatile uint32_t* abort_flag = tmem_slot + 1;  // set by the compute warps when a bounded wait gave up
+  volatile uint32_t* decay_flag = tmem_slot + 2;  // a chunk's decay product left the representable range
   const uint32_t sbase = smem_u32(smem);
 
   if (tid == 0) {
@@ -106,8 +124,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     mbar_init(bar_mma, 1);
     mbar_init(bar_state, 1);
     mbar_init(bar_drain, 1);
+    mbar_init(bar_p, 1);
     mbar_fence_init();
     *abort_flag = 0u;
+    *decay_flag = 0u;
     tma_prefetch_descriptor(&maps.r);
     tma_prefetch_descriptor(&maps.w);
     tma_prefetch_descriptor(&maps.k);
@@ -139,26 +159,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   bool tma_in_flight = true;
   uint32_t tma_parity = 0;
 
-  // 32 fp32 values (columns 32*half ..) of accumulator row `row` -> four 16-byte column chunks of the
-  // row-operand tile (hi/lo, rows = contraction index, MN-major)
-  auto store_operand_row = [&](int row, const uint32_t (&regs)[32]) {
-    uint8_t* op = smem + kOffOp + (row & 7) * 16 + (row >> 3) * kRowGroup;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 hi, lo;
-      split8(reinterpret_cast<const float*>(regs) + 8 * j, hi, lo);
-      *reinterpret_cast<uint4*>(op + (half * 4 + j) * kStride64) = hi;
-      *reinterpret_cast<uint4*>(op + kTileK64 + (half * 4 + j) * kStride64) = lo;
-    }
-  };
-
   // Fragment view of an accumulator block (tmem_ld_frag16): this thread holds rows frow0 and frow0 + 8 of its
   // quadrant and, of the 32 columns at 32*half, the pairs 8n + 2*fq + {0,1}, n = 0..3.
   const int fq = lane & 3;
   const int frow0 = quad * 16 + (lane >> 2);
-  // fragment -> hi/lo operand tile at `tile` (rows = accumulator rows, 16-byte column chunks from `chunk0` on):
-  // one 4-byte store per pair and part; the 32 lanes of a store cover 128 contiguous bytes
-  auto store_operand_frag = [&](uint32_t tile, uint32_t lo_off, int chunk0, const float (&x)[16]) {
+  // fragment -> fp16 operand tile at `tile` (rows = accumulator rows, 16-byte column chunks from `chunk0` on):
+  // one 4-byte store per pair; the 32 lanes of a store cover 128 contiguous bytes
+  auto store_frag_f16_split = [&](uint32_t tile, uint32_t lo_off, int chunk0, const float (&x)[16]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int row = frow0 + 8 * h;
@@ -166,54 +173,32 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
         uint32_t hi, lo;
-        split2(x[4 * n + 2 * h], x[4 * n + 2 * h + 1], hi, lo);
+        split2_f16(x[4 * n + 2 * h], x[4 * n + 2 * h + 1], hi, lo);
         *reinterpret_cast<uint32_t*>(dst + (chunk0 + n) * kStride64) = hi;
         *reinterpret_cast<uint32_t*>(dst + lo_off + (chunk0 + n) * kStride64) = lo;
       }
     }
   };
 
-  // ---- initial state: global -> TMEM (fp32) and -> S0 operand tile ----------------------------
   float* state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
   const bool compute_warp = warp < kWarps;
-  if (compute_warp) {
-    uint32_t regs[32];
-    if (row_lane) {
-      const float4* src = reinterpret_cast<const float4*>(state_g + arow * kHeadDim + half * 32);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 f = __ldcs(src + i);
-        regs[4 * i] = __float_as_uint(f.x);
-        regs[4 * i + 1] = __float_as_uint(f.y);
-        regs[4 * i + 2] = __float_as_uint(f.z);
-        regs[4 * i + 3] = __float_as_uint(f.w);
-      }
-      store_operand_row(arow, regs);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) regs[i] = 0u;
-    }
-    tmem_st32(tmem_lane + kColS + half * 32, regs);
-    tmem_st_wait();
-  }
 
-  constexpr uint32_t idesc_kk = instr_desc_f16(64, 64, kMajorK, kMajorK);
-  constexpr uint32_t idesc_kmn = instr_desc_f16(64, 64, kMajorK, kMajorMN);
-  constexpr uint32_t idesc_mnmn = instr_desc_f16(64, 64, kMajorMN, kMajorMN);
-  constexpr bool kVExact = std::is_same<io_t, __nv_bfloat16>::value;
-  constexpr uint32_t v_lo_off = kVExact ? 0u : kTileV;
+  constexpr uint32_t idesc_p = instr_desc_f16(64, 64, kMajorK, kMajorK, true);        // bf16 x bf16
+  constexpr uint32_t idesc_kmn = instr_desc_f16(64, 64, kMajorK, kMajorMN, false);    // fp16, A K-major, B MN-major
+  constexpr uint32_t idesc_mnmn = instr_desc_f16(64, 64, kMajorMN, kMajorMN, false);  // fp16, both MN-major
 
   // operand descriptors (fixed for the whole kernel); K-major tiles: chunk stride kStride64, row groups 128 B
   const Operand op_x1 = make_operand(sbase + kOffX1, kTileK64, 2 * kStride64, kStride64, kRowGroup);
   const Operand op_x2 = make_operand(sbase + kOffX2, kTileK64, 2 * kStride64, kStride64, kRowGroup);
+  const Operand op_x1h = make_operand(sbase + kOffX1h, 0, 2 * kStride64, kStride64, kRowGroup);
   const Operand op_x3 = make_operand(sbase + kOffX3, kTileK32, 2 * kStride64, kStride64, kRowGroup);
-  const Operand op_x4 = make_operand(sbase + kOffX4, kTileK32, 2 * kStride64, kStride64, kRowGroup);
+  const Operand op_x4 = make_operand(sbase + kOffX4, 0, 2 * kStride64, kStride64, kRowGroup);
   // MN-major tiles (rows = contraction index): row groups 128 B apart, 16-byte column chunks at the tile's stride
   const Operand op_rows = make_operand(sbase + kOffOp, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
-  const Operand op_v = make_operand(sbase + kOffV, v_lo_off, 2 * kRowGroup, kRowGroup, kStride32);
-  // [Bt; Kt] read MN-major: M = key channel, contraction = tile row (Bt rows 0..31, Kt rows 32..63)
-  const Operand op_bt = make_operand(sbase + kOffX2, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
-  const Operand op_kt = make_operand(sbase + kOffX2 + 4 * kRowGroup, kTileK64, 2 * kRowGroup, kRowGroup, kStride64);
+  const Operand op_v = make_operand(sbase + kOffV, 0, 2 * kRowGroup, kRowGroup, kStride32);
+  // Bl, Kl read MN-major as left operands: M = key channel, contraction = token row
+  const Operand op_bl = make_operand(sbase + kOffBl, 0, 2 * kRowGroup, kRowGroup, kStride32);
+  const Operand op_kl = make_operand(sbase + kOffKl, kTile32, 2 * kRowGroup, kRowGroup, kStride32);
 
   // Row order of the stacked 64-row operands [At; Rt], [A_ak; A_rk], [T; A_rb] and of their accumulators: the two
   // kinds alternate in groups of eight, token t's At-kind row at 16*(t/8) + t%8 and its Rt-kind row eight further.
@@ -226,12 +211,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tmem_ld_wait();
     uint8_t* dst = smem + kOffOp + (ftok >> 3) * kRowGroup + (ftok & 7) * 16 + fq * 4;
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      uint32_t hi, lo;
-      split2(__uint_as_float(regs[4 * n]), __uint_as_float(regs[4 * n + 1]), hi, lo);
-      *reinterpret_cast<uint32_t*>(dst + (half * 4 + n) * kStride64) = hi;
-      *reinterpret_cast<uint32_t*>(dst + kTileK64 + (half * 4 + n) * kStride64) = lo;
-    }
+    for (int n = 0; n < 4; ++n)
+      *reinterpret_cast<uint32_t*>(dst + (half * 4 + n) * kStride64) =
+          pack_f16x2(__uint_as_float(regs[4 * n]), __uint_as_float(regs[4 * n + 1]));
   };
 
   bool failed = false;
@@ -243,12 +225,14 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
   // ---- operand preparation of one chunk (decay products, scaled operands) -----------------------------------
   // It depends on the tokens only, so it runs for chunk c+1 while the tensor pipe works on chunk c's last
-  // products.  [At; Rt] goes straight to its tile (free since Q was read); [Bt; Kt] and V, whose tiles the state
-  // MMAs of chunk c still read, stay in these registers until release_operands().
-  uint32_t held_x2[16];  // per row of this thread: Bt hi, Bt lo, Kt hi, Kt lo
-  uint4 held_v_hi, held_v_lo = make_uint4(0u, 0u, 0u, 0u);
-  float2 held_lg[kChunk / kWarps];  // log2 of the inclusive decay product of this thread's rows, scan -> scaling
-  float2 held_off = make_float2(0.f, 0.f);  // ... and of the rows before them
+  // products.  The operands of P and Q go straight to their tiles (P and Q of chunk c are long finished), and so
+  // does Kl (Kl^T V of chunk c has retired once U has); V and Bl, whose tiles chunk c's products may still read,
+  // wait in registers until release_v() / release_bl().
+  uint32_t held_bl[kChunk / kWarps];  // per row of this thread: Bl, two key channels
+  uint4 held_v;
+  float2 held_g[kChunk / kWarps];  // inclusive retention product g_t of this thread's rows, scan -> scaling
+  float2 held_off = make_float2(1.f, 1.f);  // ... of the rows before them
+  float2 held_tot = make_float2(1.f, 1.f);  // ... and of the whole chunk (g_L)
   auto scan_decay = [&](int chunk) -> bool {  // first half (all compute threads; one compute barrier inside)
     const int rows = min(kChunk, len - chunk * kChunk);
     const bool ok = mbar_wait(bar_tma, tma_parity);
@@ -260,62 +244,72 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     const uint32_t* raw_w = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 1 * kRawTile);
     float2 bias2 = make_float2(0.f, 0.f);
     if (bias_g != nullptr) bias2 = make_float2(to_f32(bias_g[2 * kp]), to_f32(bias_g[2 * kp + 1]));
-    float2 run = make_float2(0.f, 0.f);
+    float2 run = make_float2(1.f, 1.f);
     float2 cum[kRowsPerWarp];
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; ++i) {
       const int t = tg * kRowsPerWarp + i;
-      const float2 w2 = unpack2<io_t>(raw_w[t * 32 + kp]);
-      float2 l;
+      float2 rho = unpack2<io_t>(raw_w[t * 32 + kp]);
       if constexpr (LOGITS) {
-        l.x = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.x + bias2.x)));
-        l.y = __fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (w2.y + bias2.y)));
-      } else {
-        l.x = fast_log2(w2.x);
-        l.y = fast_log2(w2.y);
+        rho.x = fast_exp2(__fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (rho.x + bias2.x))));
+        rho.y = fast_exp2(__fdividef(-kRateLog2e, 1.0f + fast_exp2(-kLog2e * (rho.y + bias2.y))));
       }
-      if (t >= rows) l = make_float2(0.f, 0.f);
-      run.x += l.x;
-      run.y += l.y;
+      if (t >= rows) rho = make_float2(1.f, 1.f);
+      run.x *= rho.x;
+      run.y *= rho.y;
       cum[i] = run;
     }
-    reinterpret_cast<float2*>(group_sum + tg * 64)[kp] = run;
-    // V operand: rows = token, 64 contiguous value columns (MN-major); bf16 is copied, fp16 is split
+    reinterpret_cast<float2*>(group_prod + tg * 64)[kp] = run;
+    // V operand: rows = token, 64 contiguous value columns (MN-major), converted to fp16 (exact for bf16 values
+    // inside the fp16 range)
     {
       const uint8_t* raw_v = smem + kOffRaw + 3 * kRawTile;
       const int sr = tid >> 3, vc = tid & 7;  // 256 chunks of 8 values
       uint4 q = *reinterpret_cast<const uint4*>(raw_v + sr * 128 + vc * 16);
       if (sr >= rows) q = make_uint4(0u, 0u, 0u, 0u);
-      if constexpr (kVExact) {
-        held_v_hi = q;
+      if constexpr (std::is_same<io_t, __half>::value) {
+        held_v = q;
       } else {
-        float x[8];
         const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+        uint32_t out[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f = unpack2<io_t>(words[e]);
-          x[2 * e] = f.x;
-          x[2 * e + 1] = f.y;
+          out[e] = pack_f16x2(f.x, f.y);
         }
-        split8(x, held_v_hi, held_v_lo);
+        held_v = make_uint4(out[0], out[1], out[2], out[3]);
       }
     }
     named_sync(kBarCompute, kComputeThreads);
-    float2 off = make_float2(0.f, 0.f);
+    float2 off = make_float2(1.f, 1.f), tot = make_float2(1.f, 1.f);
 #pragma unroll
-    for (int g = 0; g < kWarps - 1; ++g) {  // loads issued together; only the adds are a chain
-      const float2 sgrp = reinterpret_cast<const float2*>(group_sum + g * 64)[kp];
+    for (int g = 0; g < kWarps; ++g) {  // loads issued together; only the products are a chain
+      const float2 pgrp = reinterpret_cast<const float2*>(group_prod + g * 64)[kp];
       if (g < tg) {
-        off.x += sgrp.x;
-        off.y += sgrp.y;
+        off.x *= pgrp.x;
+        off.y *= pgrp.y;
       }
+      tot.x *= pgrp.x;
+      tot.y *= pgrp.y;
     }
     held_off = off;
+    held_tot = tot;
+    if constexpr (!LOGITS) {
+      // 1/g_t must stay inside the fp32 range (the logits form cannot produce less than 2^-28 over a chunk)
+      if (!(tot.x > 1e-36f) || !(tot.y > 1e-36f)) *decay_flag = 1u;
+    }
 #pragma unroll
-    for (int i = 0; i < kRowsPerWarp; ++i) held_lg[i] = make_float2(off.x + cum[i].x, off.y + cum[i].y);
+    for (int i = 0; i < kRowsPerWarp; ++i) held_g[i] = make_float2(off.x * cum[i].x, off.y * cum[i].y);
     return ok;
   };
-  auto scale_operands = [&](int chunk, float* gamma_dst) {  // second half: no barrier inside
+  // g_L of the chunk scan_decay() ran for last, for key channel `channel`: every warp holds all 64 values (lane l has
+  // channels 2l and 2l+1), so a shuffle delivers it without shared memory or a barrier.  All lanes must call it.
+  auto chunk_decay_of = [&](int channel) -> float {
+    const float x = __shfl_sync(0xffffffffu, held_tot.x, channel >> 1);
+    const float y = __shfl_sync(0xffffffffu, held_tot.y, channel >> 1);
+    return (channel & 1) ? y : x;
+  };
+  auto scale_operands = [&](int chunk) {  // second half: no barrier inside
     const int rows = min(kChunk, len - chunk * kChunk);
     constexpr int kRowsPerWarp = kChunk / kWarps;
     const int kp = lane, tg = warp;
@@ -323,55 +317,68 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     const uint32_t* raw_k = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 2 * kRawTile);
     const uint32_t* raw_a = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 4 * kRawTile);
     const uint32_t* raw_b = reinterpret_cast<const uint32_t*>(smem + kOffRaw + 5 * kRawTile);
-    float2 g_prev = make_float2(fast_exp2(held_off.x), fast_exp2(held_off.y));
-    uint8_t* x1 = smem + kOffX1 + (kp >> 2) * kStride64 + (kp & 3) * 4;
+    float2 g_prev = held_off;
+    const float2 gl = held_tot;
+    const uint32_t col64 = (kp >> 2) * kStride64 + (kp & 3) * 4;  // this thread's two channels in a 64-row tile
+    const uint32_t col32 = (kp >> 2) * kStride32 + (kp & 3) * 4;  // ... in a 32-row tile
+    uint8_t* x1 = smem + kOffX1 + col64;
+    uint8_t* x2 = smem + kOffX2 + col64;
+    uint8_t* x1h = smem + kOffX1h + col64;
+    uint8_t* kl = smem + kOffKl + col32;
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; ++i) {
       const int t = tg * kRowsPerWarp + i;
-      const bool live = t < rows;
-      const float2 lg = held_lg[i];
-      const float2 g = make_float2(fast_exp2(lg.x), fast_exp2(lg.y));
-      const float2 gi = make_float2(fast_exp2(-lg.x), fast_exp2(-lg.y));
+      const float2 g = held_g[i];
+      float2 gi;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(gi.x) : "f"(g.x));
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(gi.y) : "f"(g.y));
       const float2 gx = g_prev;  // exclusive product = inclusive product of the previous row
       g_prev = g;
       float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
       float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
       float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
       float2 b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
-      if (!live) {
+      if (t >= rows) {  // rows past the end of the sequence belong to somebody else (or are the loader's zero fill)
         r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
       }
       const uint32_t row_a = 2 * (t >> 3) * kRowGroup + (t & 7) * 16;  // At row of token t: 16*(t/8) + t%8
       const uint32_t row_r = row_a + kRowGroup;                        // Rt row: eight further
+      const uint32_t row_b = (t >> 3) * kRowGroup + (t & 7) * 16;      // Bt row t, Kt row 32 + t; Bl / Kl row t
       uint32_t h, l;
-      split2(a2.x * gx.x, a2.y * gx.y, h, l);
+      const float2 at = make_float2(a2.x * gx.x, a2.y * gx.y), rt = make_float2(r2.x * g.x, r2.y * g.y);
+      const float2 bt = make_float2(b2.x * gi.x, b2.y * gi.y), kt = make_float2(k2.x * gi.x, k2.y * gi.y);
+      split2(at.x, at.y, h, l);
       *reinterpret_cast<uint32_t*>(x1 + row_a) = h;
       *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_a) = l;
-      split2(r2.x * g.x, r2.y * g.y, h, l);
+      *reinterpret_cast<uint32_t*>(x1h + row_a) = pack_f16x2(at.x, at.y);
+      split2(rt.x, rt.y, h, l);
       *reinterpret_cast<uint32_t*>(x1 + row_r) = h;
       *reinterpret_cast<uint32_t*>(x1 + kTileK64 + row_r) = l;
-      split2(b2.x * gi.x, b2.y * gi.y, held_x2[4 * i], held_x2[4 * i + 1]);
-      split2(k2.x * gi.x, k2.y * gi.y, held_x2[4 * i + 2], held_x2[4 * i + 3]);
-      if (t == kChunk - 1) reinterpret_cast<float2*>(gamma_dst)[kp] = g;
+      *reinterpret_cast<uint32_t*>(x1h + row_r) = pack_f16x2(rt.x, rt.y);
+      split2(bt.x, bt.y, h, l);
+      *reinterpret_cast<uint32_t*>(x2 + row_b) = h;
+      *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_b) = l;
+      split2(kt.x, kt.y, h, l);
+      *reinterpret_cast<uint32_t*>(x2 + row_b + 4 * kRowGroup) = h;
+      *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_b + 4 * kRowGroup) = l;
+      held_bl[i] = pack_f16x2(bt.x * gl.x, bt.y * gl.y);  // Bl = b g_L / g_t: a factor <= 1
+      split2_f16(kt.x * gl.x, kt.y * gl.y, h, l);
+      *reinterpret_cast<uint32_t*>(kl + row_b) = h;
+      *reinterpret_cast<uint32_t*>(kl + kTile32 + row_b) = l;
     }
   };
-  auto release_operands = [&]() {  // [Bt; Kt] and V of the prepared chunk: registers -> tiles
+  auto release_v = [&]() {  // V of the prepared chunk: registers -> tile
+    const int sr = tid >> 3, vc = tid & 7;
+    *reinterpret_cast<uint4*>(smem + kOffV + vc * kStride32 + (sr & 7) * 16 + (sr >> 3) * kRowGroup) = held_v;
+  };
+  auto release_bl = [&]() {  // Bl of the prepared chunk: registers -> tile
     const int kp = lane, tg = warp;
-    uint8_t* x2 = smem + kOffX2 + (kp >> 2) * kStride64 + (kp & 3) * 4;
+    uint8_t* bl = smem + kOffBl + (kp >> 2) * kStride32 + (kp & 3) * 4;
 #pragma unroll
     for (int i = 0; i < kChunk / kWarps; ++i) {
       const int t = tg * (kChunk / kWarps) + i;
-      const uint32_t row_lo = (t >> 3) * kRowGroup + (t & 7) * 16;
-      const uint32_t row_hi = ((t + 32) >> 3) * kRowGroup + (t & 7) * 16;
-      *reinterpret_cast<uint32_t*>(x2 + row_lo) = held_x2[4 * i];
-      *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_lo) = held_x2[4 * i + 1];
-      *reinterpret_cast<uint32_t*>(x2 + row_hi) = held_x2[4 * i + 2];
-      *reinterpret_cast<uint32_t*>(x2 + kTileK64 + row_hi) = held_x2[4 * i + 3];
+      *reinterpret_cast<uint32_t*>(bl + (t >> 3) * kRowGroup + (t & 7) * 16) = held_bl[i];
     }
-    const int sr = tid >> 3, vc = tid & 7;
-    uint8_t* dst = smem + kOffV + vc * kStride32 + (sr & 7) * 16 + (sr >> 3) * kRowGroup;
-    *reinterpret_cast<uint4*>(dst) = held_v_hi;
-    if constexpr (!kVExact) *reinterpret_cast<uint4*>(dst + kTileV) = held_v_lo;
   };
 
   uint32_t mma_phase = 0;  // completed phases of bar_mma, counted the same way by every compute thread
@@ -386,26 +393,60 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     // =====================================================================================================
     // chunk 0 is prepared up front; afterwards every chunk prepares its successor
     bad |= !scan_decay(0);
-    scale_operands(0, gamma_l);
-    release_operands();
+    scale_operands(0);
+    release_v();
+    release_bl();
+    // ---- initial state: global -> S0 operand tile (fp16) and -> TMEM (fp32, already times g_L of chunk 0) ----
+    {
+      uint32_t regs[32];
+      const float g0 = chunk_decay_of(arow);
+      if (row_lane) {
+        const float4* src = reinterpret_cast<const float4*>(state_g + arow * kHeadDim + half * 32);
+        uint8_t* op = smem + kOffOp + (arow & 7) * 16 + (arow >> 3) * kRowGroup;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 f0 = __ldcs(src + 2 * j), f1 = __ldcs(src + 2 * j + 1);
+          uint32_t hi[4], lo[4];
+          split2_f16(f0.x, f0.y, hi[0], lo[0]);
+          split2_f16(f0.z, f0.w, hi[1], lo[1]);
+          split2_f16(f1.x, f1.y, hi[2], lo[2]);
+          split2_f16(f1.z, f1.w, hi[3], lo[3]);
+          *reinterpret_cast<uint4*>(op + (half * 4 + j) * kStride64) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(op + kTileK64 + (half * 4 + j) * kStride64) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          regs[8 * j + 0] = __float_as_uint(f0.x * g0);
+          regs[8 * j + 1] = __float_as_uint(f0.y * g0);
+          regs[8 * j + 2] = __float_as_uint(f0.z * g0);
+          regs[8 * j + 3] = __float_as_uint(f0.w * g0);
+          regs[8 * j + 4] = __float_as_uint(f1.x * g0);
+          regs[8 * j + 5] = __float_as_uint(f1.y * g0);
+          regs[8 * j + 6] = __float_as_uint(f1.z * g0);
+          regs[8 * j + 7] = __float_as_uint(f1.w * g0);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) regs[i] = 0u;
+      }
+      tmem_st32(tmem_lane + kColS + half * 32, regs);
+      tmem_st_wait();
+    }
     fence_proxy_async_smem();
     tcgen05_fence_before_sync();
     failed = named_sync_or(kBarCompute, kComputeThreads, bad);
     if (failed && tid == 0) *abort_flag = 1u;
-    named_arrive(kBarOperands, kThreads);  // [At; Rt], [Bt; Kt], V of chunk 0 are in place -> P
+    named_arrive(kBarOperands, kThreads);  // the operands of P for chunk 0 are in place -> P
     if (!failed) {
-      named_arrive(kBarState, kThreads);   // ... and so is S0 -> Q, then the next chunk's load
+      named_arrive(kBarState, kThreads);   // ... and so are S0 and the scaled state -> Q, then the next chunk's load
       if (n_chunks > 1) tma_in_flight = true;
     }
 
     for (int c = 0; c < n_chunks && !failed; ++c) {
       const int rows = min(kChunk, len - c * kChunk);
       const int row0 = t_begin + c * kChunk;
+      const bool more = c + 1 < n_chunks;
       FRWKV_PHASE(0)
 
-      // ================= P = X1 X2^T (the issuer warp also starts Q = X1 S0, which runs under the read-back) ====
-      bad |= !mbar_wait(bar_mma, mma_phase & 1);
-      ++mma_phase;
+      // ================= P = X1 X2^T (issued during the previous chunk; Q = X1 S0 runs under the read-back) ====
+      bad |= !mbar_wait(bar_p, c & 1);
       tcgen05_fence_after_sync();
       FRWKV_PHASE(2)
       // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
@@ -415,15 +456,19 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         uint32_t regs[16];
         tmem_ld_frag16(tmem_lane + kColP + half * 32, regs);
         tmem_ld_wait();
+        // Column block n (columns 8n..8n+7) against this quadrant's tokens 8*quad..8*quad+7: blocks left of the
+        // diagonal are kept whole, blocks right of it are zero, only block n == quad needs the per-element test.
         float vals[16];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int limit = ftok + h;  // keep columns s < limit
+        for (int n = 0; n < 4; ++n) {
 #pragma unroll
-          for (int n = 0; n < 4; ++n) {
+          for (int h = 0; h < 2; ++h) {
+            const int limit = ftok + h;  // keep columns s < limit
 #pragma unroll
-            for (int e = 0; e < 2; ++e)
-              vals[4 * n + 2 * h + e] = 8 * n + 2 * fq + e < limit ? __uint_as_float(regs[4 * n + 2 * h + e]) : 0.0f;
+            for (int e = 0; e < 2; ++e) {
+              const float x = __uint_as_float(regs[4 * n + 2 * h + e]);
+              vals[4 * n + 2 * h + e] = n < quad ? x : (n == quad && 8 * n + 2 * fq + e < limit ? x : 0.0f);
+            }
           }
         }
         if (half == 0) {
@@ -434,13 +479,22 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 #pragma unroll
           for (int n = 0; n < 4; ++n) {
             *reinterpret_cast<float2*>(ab_row + 8 * n) = make_float2(vals[4 * n], vals[4 * n + 1]);
-            uint32_t hi, lo;
-            split2(vals[4 * n + 2], vals[4 * n + 3], hi, lo);
-            *reinterpret_cast<uint32_t*>(rb + n * kStride64) = hi;
-            *reinterpret_cast<uint32_t*>(rb + kTileK32 + n * kStride64) = lo;
+            *reinterpret_cast<uint32_t*>(rb + n * kStride64) = pack_f16x2(vals[4 * n + 2], vals[4 * n + 3]);
           }
         } else {
-          store_operand_frag(kOffX3, kTileK32, 0, vals);  // A_ak and A_rk rows, in accumulator order
+          // A_ak and A_rk rows, in accumulator order (hi/lo; a block right of the diagonal is stored as zeros)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int row = frow0 + 8 * h;
+            uint8_t* dst = smem + kOffX3 + (row >> 3) * kRowGroup + (row & 7) * 16 + fq * 4;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+              uint32_t hi = 0u, lo = 0u;
+              if (n <= quad) split2_f16(vals[4 * n + 2 * h], vals[4 * n + 2 * h + 1], hi, lo);
+              *reinterpret_cast<uint32_t*>(dst + n * kStride64) = hi;
+              *reinterpret_cast<uint32_t*>(dst + kTileK32 + n * kStride64) = lo;
+            }
+          }
         }
       }
       fence_proxy_async_smem();
@@ -541,40 +595,43 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         }
         named_sync(kBarCompute, kComputeThreads);
         FRWKV_PHASE(11)
-        // T -> the At-kind rows of X4 (hi/lo, K-major): one 16-byte chunk per thread (128 threads)
+        // T -> the At-kind rows of X4 (fp16, K-major): one 16-byte chunk per thread (128 threads)
         if (tid < 128) {
           const int t = tid & 31, cj = tid >> 5;  // a quarter-warp stores eight consecutive rows: 128 contiguous bytes
           float4 f0 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8);
           float4 f1 = *reinterpret_cast<const float4*>(ti + t * kInvLd + cj * 8 + 4);
           if (t < 16 && cj >= 2) f0 = f1 = make_float4(0.f, 0.f, 0.f, 0.f);  // block above the diagonal (holds scratch)
-          const float x[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-          uint4 hi, lo;
-          split8(x, hi, lo);
-          uint8_t* dst = smem + kOffX4 + 2 * (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64;  // At-kind row of token t
-          *reinterpret_cast<uint4*>(dst) = hi;
-          *reinterpret_cast<uint4*>(dst + kTileK32) = lo;
+          *reinterpret_cast<uint4*>(smem + kOffX4 + 2 * (t >> 3) * kRowGroup + (t & 7) * 16 + cj * kStride64) =
+              make_uint4(pack_f16x2(f0.x, f0.y), pack_f16x2(f0.z, f0.w), pack_f16x2(f1.x, f1.y), pack_f16x2(f1.z, f1.w));
         }
       }
       FRWKV_PHASE(4)
       fence_proxy_async_smem();
       tcgen05_fence_before_sync();
-      named_arrive(kBarInverse, kThreads);  // -> U = T W (rows 32..63 of this product are unused)
+      named_arrive(kBarInverse, kThreads);  // -> U = T W (the Rt-kind rows of this product are unused)
       FRWKV_PHASE(5)
 
       // while U is computed: first half of the next chunk's operand preparation (decay scan)
-      if (c + 1 < n_chunks) bad |= !scan_decay(c + 1);
+      if (more) bad |= !scan_decay(c + 1);
       bad |= !mbar_wait(bar_mma, mma_phase & 1);
       ++mma_phase;
       tcgen05_fence_after_sync();
       FRWKV_PHASE(6)
       rows_to_operand(kColU);
+      // U has retired, and with it Q += [A_ak; A_rk] V and S += Kl^T V, the last readers of this chunk's V and Kl
+      if (more) release_v();
       fence_proxy_async_smem();
       tcgen05_fence_before_sync();
-      named_arrive(kBarU, kThreads);  // -> Q[32..] += A_rb U ;  S += Bt^T U + Kt^T V
+      named_arrive(kBarU, kThreads);  // -> Q[Rt rows] += A_rb U ;  S += Bl^T U
       FRWKV_PHASE(7)
 
-      // the tensor pipe is busy with Y and S: second half of the next chunk's operand preparation meanwhile
-      if (c + 1 < n_chunks) scale_operands(c + 1, gamma_l + ((c + 1) & 1) * 64);
+      // the tensor pipe is busy with Y and S: second half of the next chunk's operand preparation meanwhile, and the
+      // next chunk's P = X1 X2^T right behind them
+      if (more) {
+        scale_operands(c + 1);
+        fence_proxy_async_smem();
+        named_arrive(kBarOperands, kThreads);
+      }
       FRWKV_PHASE(1)
       bad |= !mbar_wait(bar_mma, mma_phase & 1);
       ++mma_phase;
@@ -600,29 +657,21 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
       bad |= !mbar_wait(bar_state, c & 1);
       tcgen05_fence_after_sync();
-      // This thread has seen the state MMAs finish: their [Bt; Kt] and V tiles take the next chunk's values, and
-      // the next chunk's P = X1 X2^T, which does not need the state, starts while the state is read back.
-      if (c + 1 < n_chunks) {
-        release_operands();
-        fence_proxy_async_smem();
-        named_arrive(kBarOperands, kThreads);
-      }
-      // ---- state rows (all quadrants): S <- diag(g_L) S; keep in TMEM, refresh the S0 operand (or store) ----
+      // ---- state rows (all quadrants): S is final.  Next chunk: S -> S0 operand (fp16), g_L(next) S -> TMEM ----
       {
         uint32_t regs[16];
         tmem_ld_frag16(tmem_lane + kColS + half * 32, regs);
         tmem_ld_wait();
-        const float* gamma_c = gamma_l + (c & 1) * 64;
-        const float gl[2] = {gamma_c[frow0], gamma_c[frow0 + 8]};
         float x[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          x[i] = __uint_as_float(regs[i]) * gl[(i >> 1) & 1];
-          regs[i] = __float_as_uint(x[i]);
-        }
-        if (c + 1 < n_chunks) {
+        for (int i = 0; i < 16; ++i) x[i] = __uint_as_float(regs[i]);
+        if (more) {
+          release_bl();  // S += Bl^T U, the last reader of this chunk's Bl, has retired
+          const float gl[2] = {chunk_decay_of(frow0), chunk_decay_of(frow0 + 8)};  // g_L of the next chunk
+#pragma unroll
+          for (int i = 0; i < 16; ++i) regs[i] = __float_as_uint(x[i] * gl[(i >> 1) & 1]);
           tmem_st_frag16(tmem_lane + kColS + half * 32, regs);
-          store_operand_frag(kOffOp, kTileK64, half * 4, x);
+          store_frag_f16_split(kOffOp, kTileK64, half * 4, x);
           tmem_st_wait();
         } else {
 #pragma unroll
@@ -634,7 +683,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
           }
         }
       }
-      if (c + 1 < n_chunks) {
+      if (more) {
         fence_proxy_async_smem();
         tcgen05_fence_before_sync();
         named_arrive(kBarState, kThreads);  // S0 of the next chunk is in place -> Q, then the load after next
@@ -643,7 +692,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       failed = named_sync_or(kBarCompute, kComputeThreads, bad);
       if (failed) {
         if (tid == 0) *abort_flag = 1u;
-        if (c + 1 < n_chunks) named_arrive(kBarMasks, kThreads);  // the issuer warp's next hand-off
+        if (more) named_arrive(kBarMasks, kThreads);  // the issuer warp's next hand-off
         break;
       }
       FRWKV_PHASE(9)
@@ -660,26 +709,29 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
-        issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_kk, false);
-        if (c != p.skip_commit_chunk) mma_commit(bar_mma);  // P: runs while the previous chunk's state is read back
+        issue_gemm<true, true, 4>(tmem + kColP, op_x1, op_x2, idesc_p, false);
+#ifdef FRWKV_TEST_HOOKS
+        if (c != p.skip_commit_chunk)
+#endif
+          mma_commit(bar_p);  // P: queued behind the previous chunk's Y and S products
       }
       __syncwarp();
       named_sync(kBarState, kThreads);
       if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
-        issue_gemm<true, true, 4>(tmem + kColQ, op_x1, op_rows, idesc_kmn, false);  // Q = X1 S0: under the P read-back
+        issue_gemm<false, true, 4>(tmem + kColQ, op_x1h, op_rows, idesc_kmn, false);  // Q = X1 S0: under the P read-back
       }
       __syncwarp();
       named_sync(kBarMasks, kThreads);
       if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
-        issue_gemm<true, !kVExact, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
+        issue_gemm<true, false, 2>(tmem + kColQ, op_x3, op_v, idesc_kmn, true);
         mma_commit(bar_mma);  // Q complete (commits track every earlier MMA of the thread)
-        // S += Kt^T V does not need U: it runs now, while the compute warps invert and the pipe would be idle, instead
+        // S += Kl^T V does not need U: it runs now, while the compute warps invert and the pipe would be idle, instead
         // of at the end of the chunk where the state products are waited for
-        issue_gemm<true, !kVExact, 2>(tmem + kColS, op_kt, op_v, idesc_mnmn, true);
+        issue_gemm<true, false, 2>(tmem + kColS, op_kl, op_v, idesc_mnmn, true);
         // the next chunk's tokens, most of a chunk ahead of their use; issued here because nothing waits for it,
         // whereas the products above and below are on the compute warps' critical path
         if (c + 1 < n_chunks) issue_tma(c + 1);
@@ -689,7 +741,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
-        issue_gemm<true, true, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
+        issue_gemm<false, false, 2>(tmem + kColU, op_x4, op_rows, idesc_kmn, false);
         mma_commit(bar_mma);
       }
       __syncwarp();
@@ -697,10 +749,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       if (*abort_flag != 0u) break;
       if (lane == 0) {
         tcgen05_fence_after_sync();
-        issue_gemm<true, true, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
+        issue_gemm<false, false, 2>(tmem + kColQ, op_x4, op_rows, idesc_kmn, true);
         mma_commit(bar_mma);  // Y is complete when this one arrives ...
-        issue_gemm<true, true, 2>(tmem + kColS, op_bt, op_rows, idesc_mnmn, true);
-        mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMAs
+        issue_gemm<false, false, 2>(tmem + kColS, op_bl, op_rows, idesc_mnmn, true);
+        mma_commit(bar_state);  // ... and S when this one does: the y read-back overlaps the state MMA
       }
       __syncwarp();
     }
@@ -714,19 +766,45 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   }
 
   if (failed) {
-    if (tid == 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 1);
+    if (tid == 0 && p.error_flag != nullptr) atomicOr(p.error_flag, kErrorWait);
     if (tma_in_flight) mbar_wait(bar_tma, tma_parity, 200000u);  // bounded drain of the load in flight
+    // fail closed even for a caller that passed no error flag: this (sequence, head)'s output rows become NaN (its
+    // state slot keeps the value it had before the call: the state is only written after the last chunk)
+    if (compute_warp) {
+      const float qnan = __int_as_float(0x7fffffff);
+      for (long long i = tid; i < static_cast<long long>(len) * kHeadDim; i += kComputeThreads) {
+        const size_t at = (static_cast<size_t>(t_begin + i / kHeadDim) * p.heads + head) * kHeadDim + i % kHeadDim;
+        static_cast<io_t*>(p.y)[at] = from_f32<io_t>(qnan);
+        if (p.y_f32 != nullptr) p.y_f32[at] = qnan;
+      }
+    }
   }
   tcgen05_fence_before_sync();
   __syncthreads();
+  if (tid == 0 && *decay_flag != 0u && p.error_flag != nullptr) atomicOr(p.error_flag, kErrorDecay);
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// The shared-memory attribute is set once per device and kernel instance, not on every call.
+template <typename io_t, bool LOGITS>
+int prepare_kernel() {
+  static bool done[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return check_launch("cudaGetDevice");
+  if (!done[device]) {
+    if (cudaFuncSetAttribute(wkv7_chunk32_tc_kernel<io_t, LOGITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes) != cudaSuccess)
+      return check_launch("wkv7_chunk32_tc_kernel shared-memory attribute");
+    done[device] = true;  // benign race: two threads may both set the same attribute
+  }
+  return FRWKV_OK;
 }
 
 template <typename io_t>
 int launch_typed32(const ChunkParams& p, const Maps& maps, bool logits, cudaStream_t stream) {
+  const int rc = logits ? prepare_kernel<io_t, true>() : prepare_kernel<io_t, false>();
+  if (rc != FRWKV_OK) return rc;
   auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true> : wkv7_chunk32_tc_kernel<io_t, false>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-    return check_launch("wkv7_chunk32_tc_kernel shared-memory attribute");
   const long long ctas = static_cast<long long>(p.n_seq) * p.heads;
   if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: too many (sequence, head) pairs");
   kernel<<<static_cast<unsigned>(ctas), kThreads, kSmemBytes, stream>>>(p, maps);
@@ -734,6 +812,15 @@ int launch_typed32(const ChunkParams& p, const Maps& maps, bool logits, cudaStre
 }
 
 }  // namespace
+
+#ifdef FRWKV_TEST_HOOKS
+namespace chunk {
+int& test_skip_commit_chunk() {
+  static int chunk_index = -1;
+  return chunk_index;
+}
+}  // namespace chunk
+#endif
 
 int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
@@ -743,11 +830,18 @@ int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* st
   chunk::Maps maps;
   const int map_rc = chunk::make_maps(&maps, r, w, k, v, a, b, total_tokens, heads, bf16, kChunk);
   if (map_rc != FRWKV_OK) return map_rc;
-  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from,
-                       chunk::test_skip_commit_chunk()};
+  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from};
+#ifdef FRWKV_TEST_HOOKS
+  p.skip_commit_chunk = chunk::test_skip_commit_chunk();
+#endif
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
   if (bf16) return launch_typed32<__nv_bfloat16>(p, maps, logits, stream);
   return launch_typed32<__half>(p, maps, logits, stream);
 }
 
 }  // namespace frwkv
+
+#ifdef FRWKV_TEST_HOOKS
+// Test build only: the chunk whose P commit the next prefill launches leave out (-1 = none).
+extern "C" void frwkv_sm100_test_skip_commit(int chunk_index) { frwkv::chunk::test_skip_commit_chunk() = chunk_index; }
+#endif

@@ -1,11 +1,12 @@
-// Pieces shared by the tensor-core chunk kernels (64-row and 32-row chunks): parameters, the
-// hi/lo operand split, operand descriptors and MMA issue, TMA tensor-map creation.
+// Pieces of the tensor-core chunk kernel: parameters, the hi/lo operand splits (bf16 and fp16),
+// operand descriptors and MMA issue, TMA tensor-map creation (cached per tensor).
 #pragma once
 
 #include "../../common.cuh"
 #include "../../tcgen05.cuh"
 
-#include <cstdlib>
+#include <cstring>
+#include <mutex>
 #include <type_traits>
 
 namespace frwkv {
@@ -29,12 +30,17 @@ __device__ unsigned long long g_phase_ticks[16];
 #define FRWKV_PHASE(i)
 #endif
 
-// Test hook for the bounded waits: FRWKV_TEST_SKIP_COMMIT=<chunk index> makes the 32-row kernel leave out one
-// tcgen05.commit, so that the wait on it runs out and the failure path (error flag, no hang) can be exercised.
-inline int test_skip_commit_chunk() {
-  const char* e = std::getenv("FRWKV_TEST_SKIP_COMMIT");
-  return e != nullptr ? std::atoi(e) : -1;
-}
+// Test hook for the bounded waits, compiled only into the test build of the library (FRWKV_TEST_HOOKS):
+// frwkv_sm100_test_skip_commit(chunk) makes the kernel leave out one tcgen05.commit, so that the wait on it
+// runs out and the failure path (error flag, no hang) can be exercised.  The product library has neither
+// the setter nor the check in its kernel.
+#ifdef FRWKV_TEST_HOOKS
+int& test_skip_commit_chunk();
+#endif
+
+// bits of *error_flag
+constexpr int kErrorWait = 1;   // a bounded wait gave up
+constexpr int kErrorDecay = 2;  // the decay product of one chunk left the fp32 range (retention mode only)
 
 struct ChunkParams {
   const int* cu;
@@ -49,7 +55,9 @@ struct ChunkParams {
   float scale;
   const int* order;  // CTA rank -> sequence, longest first (nullptr: natural order)
   int len_from;      // > 0: only sequences at least this long (shorter ones go to the recurrence kernel)
-  int skip_commit_chunk;  // test hook (FRWKV_TEST_SKIP_COMMIT): chunk whose first MMA commit is left out, -1 = none
+#ifdef FRWKV_TEST_HOOKS
+  int skip_commit_chunk;  // chunk whose first MMA commit is left out, -1 = none
+#endif
 };
 
 struct Maps {
@@ -91,6 +99,19 @@ __device__ __forceinline__ void split8(const float* x, uint4& hi, uint4& lo) {
   }
   hi = make_uint4(h[0], h[1], h[2], h[3]);
   lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// fp16 operands: one rounding, or a hi/lo pair (22 significant bits).  A value beyond the fp16 range becomes
+// inf (and the lo part -inf), so an overflow shows as NaN in the output instead of a silently saturated term.
+__device__ __forceinline__ uint32_t pack_f16x2(float lo_elem, float hi_elem) {
+  __half2 h = __floats2half2_rn(lo_elem, hi_elem);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void split2_f16(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  const __half2 h = __floats2half2_rn(x0, x1);
+  const float2 back = __half22float2(h);
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  lo = pack_f16x2(x0 - back.x, x1 - back.y);
 }
 
 template <typename io_t> __device__ __forceinline__ float2 unpack2(uint32_t packed);
@@ -161,12 +182,45 @@ inline int make_map(CUtensorMap* map, const void* base, int total_tokens, int he
 }
 
 
+// Encoding a tensor map is a driver call of a few microseconds; a serving loop calls prefill with the same six
+// buffers over and over, so the encoded maps are kept in a small cache keyed by (address, shape, dtype, box).
+// A map depends on nothing else, so a stale entry for a freed and re-allocated address is still correct.
+struct MapKey {
+  const void* base;
+  int total_tokens, heads, bf16, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && total_tokens == o.total_tokens && heads == o.heads && bf16 == o.bf16 &&
+           box_rows == o.box_rows;
+  }
+};
+inline int cached_map(CUtensorMap* map, const void* base, int total_tokens, int heads, bool bf16, int box_rows) {
+  constexpr int kEntries = 96;
+  static std::mutex mutex;
+  static MapKey keys[kEntries];
+  static CUtensorMap maps[kEntries];
+  static int used = 0, next = 0;
+  const MapKey key{base, total_tokens, heads, bf16 ? 1 : 0, box_rows};
+  std::lock_guard<std::mutex> lock(mutex);
+  for (int i = 0; i < used; ++i) {
+    if (keys[i] == key) {
+      std::memcpy(map, &maps[i], sizeof(CUtensorMap));
+      return FRWKV_OK;
+    }
+  }
+  const int rc = make_map(map, base, total_tokens, heads, bf16, box_rows);
+  if (rc != FRWKV_OK) return rc;
+  const int slot = used < kEntries ? used++ : (next = (next + 1) % kEntries);
+  keys[slot] = key;
+  std::memcpy(&maps[slot], map, sizeof(CUtensorMap));
+  return FRWKV_OK;
+}
+
 inline int make_maps(Maps* maps, const void* r, const void* w, const void* k, const void* v, const void* a,
                      const void* b, int total_tokens, int heads, bool bf16, int box_rows) {
   const void* srcs[6] = {r, w, k, v, a, b};
   CUtensorMap* dsts[6] = {&maps->r, &maps->w, &maps->k, &maps->v, &maps->a, &maps->b};
   for (int i = 0; i < 6; ++i) {
-    const int rc = make_map(dsts[i], srcs[i], total_tokens, heads, bf16, box_rows);
+    const int rc = cached_map(dsts[i], srcs[i], total_tokens, heads, bf16, box_rows);
     if (rc != FRWKV_OK) return rc;
   }
   return FRWKV_OK;

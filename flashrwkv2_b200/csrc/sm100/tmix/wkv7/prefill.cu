@@ -2,23 +2,18 @@
 // and the register-streaming recurrence.
 #include "../../common.cuh"
 
-#include <cstdlib>
 
 namespace frwkv {
 
 int check_wkv7_arguments(const char* who, const int32_t* cu, const int32_t* slots, float* pool,
                          const void* r, const void* w, const void* k, const void* v, const void* a,
-                         const void* b, const void* bias, void* y, int n_seq, int total_tokens, int heads,
-                         int io_dtype, int decay_mode, float scale);
+                         const void* b, const void* bias, void* y, const float* y_f32, int n_seq, int total_tokens,
+                         int heads, int io_dtype, int decay_mode, float scale);
 int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool,
                             const void* r, const void* w, const void* k, const void* v, const void* a,
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
                             int max_seqlen, int parts_override, int len_below, cudaStream_t stream);
-int launch_chunk64_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
-                      const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
-                      void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, const int32_t* order, int len_from, int32_t* error_flag, cudaStream_t stream);
 int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
@@ -59,8 +54,7 @@ size_t chunk_tc_workspace_bytes(int n_seq, int, int) {
   return n_seq > 1 && n_seq <= kMaxOrdered ? static_cast<size_t>(n_seq) * sizeof(int) : 0;
 }
 
-// Chunk length of the tensor-core kernel: 32-row chunks keep two CTAs resident per SM, 64-row chunks
-// do more work per barrier.  FRWKV_PREFILL_CHUNK=32|64 overrides the default (tuning / test hook).
+// The tensor-core path: optional longest-first ranking, then the 32-row chunk kernel.
 int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                     const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
@@ -78,12 +72,7 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
     if (rc != FRWKV_OK) return rc;
     order = static_cast<const int32_t*>(workspace);
   }
-  int chunk = 32;
-  if (const char* e = std::getenv("FRWKV_PREFILL_CHUNK")) chunk = std::atoi(e);
-  if (chunk == 32)
-    return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                             io_dtype, decay_mode, scale, order, len_from, error_flag, stream);
-  return launch_chunk64_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
+  return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
                            io_dtype, decay_mode, scale, order, len_from, error_flag, stream);
 }
 
@@ -101,7 +90,7 @@ extern "C" int frwkv_sm100_wkv7_prefill(
     size_t workspace_bytes, int32_t* error_flag, void* stream) {
   using namespace frwkv;
   int rc = check_wkv7_arguments("wkv7_prefill", cu_seqlens, slots, state_pool, r, w, k, v, a, b, decay_bias, y,
-                                n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
+                                y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
   if (rc != FRWKV_OK) return rc;
   if (strategy != FRWKV_PREFILL_AUTO && strategy != FRWKV_PREFILL_RECURRENT && strategy != FRWKV_PREFILL_CHUNK_TC)
     return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: unknown strategy %d", strategy);

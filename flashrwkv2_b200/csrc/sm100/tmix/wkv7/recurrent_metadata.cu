@@ -47,7 +47,10 @@ __global__ void __launch_bounds__(kThreads) validate_metadata_kernel(
   const int* vcu = cu_snap ? cu_snap : cu;
   const int* vslots = cu_snap ? slots_snap : slots;
   const int tok = s_tok, seq = s_seq;
-  if (tid == 0 && s_err == 0 && (vcu[0] != 0 || vcu[seq] != tok)) atomicOr(&s_err, FRWKV_META_BAD_ENDPOINT);
+  // The end-point test looks at the error word, so it is finished (barrier) before any thread can add a range or
+  // slot error to it: whether the end-point bit appears beside those never depends on timing.
+  if (tid == 0 && s_err == 0 && (vcu[0] != 0 || vcu[seq] != tok)) s_err = FRWKV_META_BAD_ENDPOINT;
+  __syncthreads();
   int err = 0;
   for (int i = tid; i < seq; i += kThreads) {
     const int lo = vcu[i], hi = vcu[i + 1];

@@ -228,11 +228,28 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
   for (int i = 0; i < RPL; ++i) __stcs(reinterpret_cast<float4*>(sbase + i * kHeadDim), S[i]);
 }
 
-// FRWKV_PDL=0 turns programmatic dependent launch off (tuning / debugging hook).
+// Tuning hooks, read from the environment once per process (not on every launch):
+// FRWKV_PDL=0 turns programmatic dependent launch off; FRWKV_RECURRENT_PARTS=2|4|8 forces the column split.
 inline bool pdl_enabled() {
-  const char* e = std::getenv("FRWKV_PDL");
-  return e == nullptr || std::atoi(e) != 0;
+  static const bool enabled = [] {
+    const char* e = std::getenv("FRWKV_PDL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return enabled;
 }
+inline int parts_from_environment() {
+  static const int parts = [] {
+    const char* e = std::getenv("FRWKV_RECURRENT_PARTS");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  return parts;
+}
+#ifdef FRWKV_TEST_HOOKS
+int& test_recurrent_parts() {  // test build only: column split forced by the next launches (0 = none)
+  static int parts = 0;
+  return parts;
+}
+#endif
 
 template <typename io_t, int PARTS, bool PREFETCH>
 int launch(const RecurrentParams& p, bool logits, cudaStream_t stream) {
@@ -275,8 +292,8 @@ int dispatch_parts(const RecurrentParams& p, bool logits, int parts, bool prefet
 // Shared argument checks of the recurrent and prefill entries.
 int check_wkv7_arguments(const char* who, const int32_t* cu, const int32_t* slots, float* pool,
                          const void* r, const void* w, const void* k, const void* v, const void* a,
-                         const void* b, const void* bias, void* y, int n_seq, int total_tokens, int heads,
-                         int io_dtype, int decay_mode, float scale) {
+                         const void* b, const void* bias, void* y, const float* y_f32, int n_seq, int total_tokens,
+                         int heads, int io_dtype, int decay_mode, float scale) {
   if (!cu || !slots || !pool || !r || !w || !k || !v || !a || !b || !y)
     return fail(FRWKV_ERR_ARGUMENT, "%s: cu_seqlens, slots, state_pool, r, w, k, v, a, b and y must be non-null", who);
   if (n_seq <= 0 || n_seq > 65535)
@@ -291,7 +308,9 @@ int check_wkv7_arguments(const char* who, const int32_t* cu, const int32_t* slot
     return fail(FRWKV_ERR_ARGUMENT, "%s: decay_bias only applies to decay logits", who);
   if (!(scale == scale) || scale - scale != 0.0f)
     return fail(FRWKV_ERR_ARGUMENT, "%s: scale must be finite", who);
-  const void* ptrs[] = {r, w, k, v, a, b, y, pool};
+  // every tensor is accessed with 16-byte vectors (decay_bias and y_f32 too, when given): a misaligned view
+  // is rejected here instead of faulting on the device
+  const void* ptrs[] = {r, w, k, v, a, b, y, pool, bias, y_f32};
   for (const void* q : ptrs)
     if ((reinterpret_cast<uintptr_t>(q) & 15) != 0)
       return fail(FRWKV_ERR_ARGUMENT, "%s: tensors must be 16-byte aligned", who);
@@ -313,10 +332,10 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
   const long long pairs = static_cast<long long>(n_seq) * heads;
   if (max_seqlen <= 0 || max_seqlen > 2) parts = 4;
   if (max_seqlen <= 0 || max_seqlen > 64 || pairs < 148LL * 4) parts = 8;
-  if (parts_override == 0) {  // tuning / test hook: force the column split
-    const char* e = std::getenv("FRWKV_RECURRENT_PARTS");
-    if (e != nullptr) parts_override = std::atoi(e);
-  }
+  if (parts_override == 0) parts_override = parts_from_environment();
+#ifdef FRWKV_TEST_HOOKS
+  if (test_recurrent_parts() != 0) parts_override = test_recurrent_parts();
+#endif
   if (parts_override == 2 || parts_override == 4 || parts_override == 8) parts = parts_override;
   const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
@@ -336,9 +355,14 @@ extern "C" int frwkv_sm100_wkv7_recurrent(
     int io_dtype, int decay_mode, float scale, int max_seqlen, void* stream) {
   using namespace frwkv;
   int rc = check_wkv7_arguments("wkv7_recurrent", cu_seqlens, slots, state_pool, r, w, k, v, a, b, decay_bias,
-                                y, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
+                                y, y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
   if (rc != FRWKV_OK) return rc;
   return launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
                                  n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0,
                                  static_cast<cudaStream_t>(stream));
 }
+
+#ifdef FRWKV_TEST_HOOKS
+// Test build only: force the column split (2, 4 or 8; 0 = automatic) of the recurrence kernel's next launches.
+extern "C" void frwkv_sm100_test_recurrent_parts(int parts) { frwkv::test_recurrent_parts() = parts; }
+#endif

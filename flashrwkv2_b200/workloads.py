@@ -28,6 +28,7 @@ class Workload:
     state_std: float  # 0 => zero initial state
     kind: str  # "decode" | "prefill" | "cpu"
     tensors: dict = field(default_factory=dict)
+    sequences: list = field(default_factory=list)  # indices of these sequences in the whole (unsharded) batch
 
     @property
     def total_tokens(self) -> int:
@@ -39,25 +40,36 @@ class Workload:
 
 
 def token_tensors(total: int, heads: int, *, generator: torch.Generator, device, dtype,
-                  block_tokens: int = 1 << 15) -> dict[str, torch.Tensor]:
+                  block_tokens: int = 1 << 15, keep: torch.Tensor | None = None) -> dict[str, torch.Tensor]:
     """r, w (retention), k, v, a, b of shape [total, heads, 64] in ``dtype``.
-    Generated in blocks of tokens so that the fp32 intermediates stay small."""
-    out = {n: torch.empty((total, heads, 64), device=device, dtype=dtype) for n in "rwkvab"}
+    Generated in blocks of tokens so that the fp32 intermediates stay small.  With ``keep`` (a bool
+    mask over the ``total`` rows) the whole batch is still drawn, block by block, from the one
+    generator, but only the marked rows are stored: a shard is a slice of the one seeded batch."""
+    kept = total if keep is None else int(keep.sum().item())
+    out = {n: torch.empty((kept, heads, 64), device=device, dtype=dtype) for n in "rwkvab"}
+    at = 0
     for lo in range(0, total, block_tokens):
         hi = min(total, lo + block_tokens)
         shape = (hi - lo, heads, 64)
+        rows = None if keep is None else keep[lo:hi].nonzero().squeeze(1)
+        count = hi - lo if rows is None else int(rows.numel())
 
         def randn():
             return torch.randn(shape, generator=generator, device=device, dtype=torch.float32)
 
-        out["r"][lo:hi] = randn().to(dtype)
-        out["k"][lo:hi] = randn().to(dtype)
-        out["v"][lo:hi] = randn().to(dtype)
+        def put(name, block):
+            if count:
+                out[name][at:at + count] = (block if rows is None else block.index_select(0, rows)).to(dtype)
+
+        put("r", randn())
+        put("k", randn())
+        put("v", randn())
         x = torch.rand(shape, generator=generator, device=device, dtype=torch.float32) * 4.5 - 5.0
-        out["w"][lo:hi] = torch.exp(-torch.exp(x)).to(dtype)
+        put("w", torch.exp(-torch.exp(x)))
         kk = torch.nn.functional.normalize(randn(), dim=-1)
-        out["a"][lo:hi] = (-kk).to(dtype)
-        out["b"][lo:hi] = (kk * torch.sigmoid(randn())).to(dtype)
+        put("a", -kk)
+        put("b", kk * torch.sigmoid(randn()))
+        at += count
     return out
 
 
@@ -91,33 +103,47 @@ def make_workload(name: str, *, device="cpu", n_seq: int | None = None, seq_len:
                   heads: int | None = None, rank: int = 0, world: int = 1,
                   with_tensors: bool = True) -> Workload:
     """Build one of c0, c1, c2, c3, c4_decode, c4_prefill.  ``n_seq`` / ``seq_len`` /
-    ``heads`` shrink a configuration for parity tests.  With ``world > 1`` only the
-    sequences :func:`flashrwkv2_b200.sharding.shard_sequences` assigns to ``rank`` are
-    generated (each rank seeds with ``seed * 1000 + rank``)."""
+    ``heads`` shrink a configuration for parity tests.  With ``world > 1`` the rank keeps the
+    sequences :func:`flashrwkv2_b200.sharding.shard_sequences` assigns to it: every rank draws
+    the whole batch from the same seed, block by block, and stores only its own rows and state
+    slots, so the union of the shards is exactly the single-GPU batch."""
     base_n, base_t, base_h, dtype, seed, std, kind = _SPECS[name]
     h = base_h if heads is None else heads
     if name == "c3":
-        lengths = _lengths(name, seed, n_seq, seq_len)
+        all_lengths = _lengths(name, seed, n_seq, seq_len)
     else:
-        lengths = [base_t if seq_len is None else seq_len] * (base_n if n_seq is None else n_seq)
+        all_lengths = [base_t if seq_len is None else seq_len] * (base_n if n_seq is None else n_seq)
+    mine = list(range(len(all_lengths)))
     if world > 1:
         from .sharding import shard_sequences
 
-        mine = shard_sequences(lengths, world)[rank]
-        lengths = [lengths[i] for i in mine]
-        seed = seed * 1000 + rank
+        mine = shard_sequences(all_lengths, world)[rank]
+    lengths = [all_lengths[i] for i in mine]
     wl = Workload(name, lengths, h, dtype, seed, std, kind)
+    wl.sequences = mine
     if not with_tensors:
         return wl
     g = torch.Generator(device=device).manual_seed(seed)
-    total = wl.total_tokens
-    wl.tensors = token_tensors(total, h, generator=g, device=device, dtype=dtype)
+    total = int(sum(all_lengths))
+    keep = None
+    if world > 1:
+        starts = [0]
+        for length in all_lengths:
+            starts.append(starts[-1] + length)
+        keep = torch.zeros(total, dtype=torch.bool, device=device)
+        for i in mine:
+            keep[starts[i]:starts[i + 1]] = True
+    wl.tensors = token_tensors(total, h, generator=g, device=device, dtype=dtype, keep=keep)
     n = wl.n_seq
     if std > 0:
         pool = torch.empty((n, h, 64, 64), device=device, dtype=torch.float32)
-        for lo in range(0, n, 64):
-            hi = min(n, lo + 64)
-            pool[lo:hi] = torch.randn((hi - lo, h, 64, 64), generator=g, device=device) * std
+        local = {seq: j for j, seq in enumerate(mine)}
+        for lo in range(0, len(all_lengths), 64):
+            hi = min(len(all_lengths), lo + 64)
+            block = torch.randn((hi - lo, h, 64, 64), generator=g, device=device) * std
+            for seq in range(lo, hi):
+                if seq in local:
+                    pool[local[seq]] = block[seq - lo]
     else:
         pool = torch.zeros((n, h, 64, 64), device=device, dtype=torch.float32)
     cu = torch.zeros(n + 1, dtype=torch.int64)

@@ -50,3 +50,20 @@ def load_golden(name: str) -> dict:
 
 GOLDEN_CASES = ("recurrent_bf16", "recurrent_bf16_bias", "recurrent_fp16_bias",
                 "recurrent_bf16_long", "recurrent_bf16_unit", "rl_infctx_fp16")
+
+
+def load_testhooks():
+    """The test build of the C-ABI library (same sources, -DFRWKV_TEST_HOOKS): the product's entry points plus
+    frwkv_sm100_test_skip_commit() and frwkv_sm100_test_recurrent_parts().  Built on demand (nvcc, cached)."""
+    import ctypes
+
+    from flashrwkv2_b200 import _lib
+    from flashrwkv2_b200.build import build_testhooks
+
+    lib = ctypes.CDLL(str(build_testhooks()))
+    _lib.declare(lib)
+    lib.frwkv_sm100_test_skip_commit.restype = None
+    lib.frwkv_sm100_test_skip_commit.argtypes = [ctypes.c_int]
+    lib.frwkv_sm100_test_recurrent_parts.restype = None
+    lib.frwkv_sm100_test_recurrent_parts.argtypes = [ctypes.c_int]
+    return lib

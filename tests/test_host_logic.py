@@ -18,8 +18,7 @@ def test_backend_selection_by_capability():
     import flashrwkv2_b200 as pkg
 
     assert pkg._backend_module_name((10, 0)) == "_C_sm100"
-    assert pkg._backend_module_name((10, 3)) == "_C_sm100"
-    for capability in ((9, 0), (12, 0), (8, 0)):
+    for capability in ((9, 0), (12, 0), (8, 0), (10, 3)):  # sm_100a code does not run on later 10.x parts
         with pytest.raises(RuntimeError, match="no binary-compatible native backend"):
             pkg._backend_module_name(capability)
 
@@ -193,3 +192,49 @@ def test_lpt_sharding_properties():
         assert p["cu_seqlens"][0] == 0 and p["cu_seqlens"][-1] == p["r"].shape[0]
         assert p["state_indices"].tolist() == [slots[i].item() for i in p["sequences"]]
         assert torch.equal(p["r"][:, 0, 0], p["rows"].float())
+
+
+def test_sharded_workload_is_a_slice_of_the_one_seeded_batch():
+    """make_workload(rank, world): every rank draws the same batch and keeps its own sequences, so a run on N
+    GPUs works on exactly the inputs of the single-GPU run."""
+    from flashrwkv2_b200.sharding import shard_sequences
+    from flashrwkv2_b200.workloads import make_workload
+
+    full = make_workload("c3", n_seq=7, seq_len=50, heads=2)
+    cu = full.tensors["cu_seqlens"].tolist()
+    bins = shard_sequences(full.lengths, 3)
+    for rank in range(3):
+        part = make_workload("c3", n_seq=7, seq_len=50, heads=2, rank=rank, world=3)
+        assert part.sequences == bins[rank] and part.lengths == [full.lengths[i] for i in bins[rank]]
+        at = 0
+        for j, seq in enumerate(part.sequences):
+            n = cu[seq + 1] - cu[seq]
+            for name in "rwkvab":
+                assert torch.equal(part.tensors[name][at:at + n], full.tensors[name][cu[seq]:cu[seq + 1]])
+            assert torch.equal(part.tensors["state_pool"][j], full.tensors["state_pool"][seq])
+            at += n
+        assert part.tensors["cu_seqlens"][-1].item() == at
+    decode = [make_workload("c4_decode", n_seq=16, heads=1, rank=r, world=4) for r in range(4)]
+    assert [d.n_seq for d in decode] == [4] * 4
+
+
+def test_c_abi_rejects_misaligned_tensors_before_any_launch():
+    """Every tensor is read or written with 16-byte vectors, decay_bias and the fp32 output copy included: a
+    contiguous view at an odd offset (say flat_params[1:1+H*64]) must come back as an argument error, not reach
+    the kernel.  The pointers here are made-up numbers; a rejected call dereferences and launches nothing."""
+    from flashrwkv2_b200 import _lib
+
+    lib = _lib.load()
+    base = 0x7F0000000000
+
+    def call(entry, bias=0, y32=0, y=base + 0x8000):
+        ptrs = [base + 0x1000 * i for i in range(1, 11)]  # cu, slots, (status=0), pool, r, w, k, v, a, b
+        head = (ptrs[0], ptrs[1], 0, ptrs[2], *ptrs[3:9], bias, y, y32, 4, 4, 2, _lib.IO_BF16, _lib.DECAY_LOGITS, 1.0, 1)
+        if entry == "recurrent":
+            return lib.frwkv_sm100_wkv7_recurrent(*head, 0)
+        return lib.frwkv_sm100_wkv7_prefill(*head, _lib.PREFILL_AUTO, 0, 0, 0, 0)
+
+    for entry in ("recurrent", "prefill"):
+        for kw in (dict(bias=base + 0x9002), dict(y32=base + 0xA004), dict(y=base + 0x8008)):
+            assert call(entry, **kw) == 1, (entry, kw)
+            assert "16-byte aligned" in _lib.last_error()

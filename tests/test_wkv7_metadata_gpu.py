@@ -133,6 +133,31 @@ def test_device_validation_status_bits(kind):
     assert got[1] == 0 and got[2] == 0
 
 
+def test_endpoint_bit_beside_range_errors_is_deterministic():
+    """More than 32 sequences (so warps other than the first take part), a wrong end point and a broken range at
+    once: as in the reference (csrc/validation/recurrent_metadata.cu:83-93) the end-point test is finished before
+    any range error is recorded, so both bits are always reported, by the ordinary and by the static entry."""
+    from flashrwkv2_b200 import _lib
+
+    lib = _lib.load()
+    n = 100
+    cu_list = list(range(0, 2 * n + 1, 2))
+    cu_list[-1] += 1          # wrong end point (the declared token count is 2n)
+    cu_list[70] = cu_list[69]  # empty sequence 69 in a later warp
+    cu = torch.tensor(cu_list, dtype=torch.int32, device=DEV)
+    slots = torch.arange(n, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(20):
+        status = torch.full((3,), 77, dtype=torch.int32, device=DEV)
+        seen = torch.empty(n, dtype=torch.int32, device=DEV)
+        assert lib.frwkv_sm100_wkv7_validate_metadata(cu.data_ptr(), slots.data_ptr(), n, 2 * n, n, 2 * n, 0, 0,
+                                                      status.data_ptr(), seen.data_ptr(), 0, 0, stream) == 0
+        static = torch.full((3,), 77, dtype=torch.int32, device=DEV)
+        assert lib.frwkv_sm100_wkv7_validate_metadata_static(cu.data_ptr(), slots.data_ptr(), n, 2 * n, n, 2 * n, 0, 0,
+                                                             static.data_ptr(), 0, 0, stream) == 0
+        assert status.cpu().tolist() == [1 | 2, 0, 0] and static.cpu().tolist() == [1 | 2, 0, 0]
+
+
 def test_device_validation_accepts_valid_and_snapshots():
     from flashrwkv2_b200 import _lib
 
@@ -258,6 +283,13 @@ def test_zero_active_warmup_then_graph_replay():
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(captured, expected) and torch.equal(state, expected_state)
+    # ... and the replay is right, not merely equal to the eager launch: the CPU oracle on the same metadata
+    from oracle.wkv7_oracle import max_err_over_rms, wkv7_oracle
+
+    y_ref, pool_ref = wkv7_oracle(*(x.cpu() for x in packed), state_pool=initial.cpu(), cu_seqlens=[0, 1, 4],
+                                  state_indices=[1, 0])
+    assert max_err_over_rms(captured.float().cpu(), y_ref) <= 5e-3  # fp16 rounding of y
+    assert max_err_over_rms(state.cpu(), pool_ref) <= 1e-5
 
     # live metadata rewrite: one active sequence on slot 0
     state.copy_(initial)

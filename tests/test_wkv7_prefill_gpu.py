@@ -3,8 +3,10 @@
 Gate (bf16 / fp16 tokens): max|d|/RMS <= 5e-3 on the fp32 y (`output_f32`, the output
 before rounding) and on the final state; the rounded y is exactly the rounding of that fp32
 y and within the reference's relative-RMSE gate for its chunk operator (7e-3 on y, 8e-3 on
-the state: rwkv-rs/FlashRWKV2 tests/fixtures/tolerances-v1.json:13-17).  The kernel's hi/lo
-operand split leaves it far inside these gates; TIGHT documents what it actually achieves.
+the state: rwkv-rs/FlashRWKV2 tests/fixtures/tolerances-v1.json:13-17).  The kernel's operand
+precision (bf16 hi/lo for the one product with unbounded operands, fp16 with one or two terms for the
+rest) is chosen to stay a factor of two inside the gate: it measures 1.2e-3 .. 2.2e-3, and TIGHT
+(3e-3) is what the small cases here are held to.
 """
 
 from __future__ import annotations
@@ -19,7 +21,7 @@ from oracle.wkv7_oracle import max_err_over_rms, relative_rmse
 pytestmark = pytest.mark.gpu
 
 GATE = 5e-3
-TIGHT = 5e-4
+TIGHT = 3e-3
 DEV = "cuda"
 
 
@@ -248,16 +250,59 @@ def test_auto_strategy_splits_a_mixed_batch_by_length():
     assert max_err_over_rms(y32[short_rows], y_ref[short_rows]) <= 1e-5
 
 
-def test_bounded_wait_reports_instead_of_hanging(monkeypatch):
-    """A tcgen05.commit that never comes (test hook FRWKV_TEST_SKIP_COMMIT): the waiting warps give up after about
-    a second, the CTA raises the error flag and leaves in order (every warp, the MMA-issuing one included), and the
-    device stays usable for the next call."""
+def _run_tc_c_abi(lib, case):
+    """The tensor-core prefill through the C ABI of `lib` (the product library or its test build)."""
+    from flashrwkv2_b200 import _lib
+
+    d = _to_dev(case)
+    pool = d["state_pool"].clone()
+    y = torch.empty_like(d["v"])
+    y32 = torch.empty(d["v"].shape, dtype=torch.float32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n_seq, (total, heads, _) = d["state_indices"].numel(), d["v"].shape
+    io = _lib.IO_BF16 if d["v"].dtype == torch.bfloat16 else _lib.IO_FP16
+    mode = _lib.DECAY_RETENTION if case.get("decay_mode") == "retention" else _lib.DECAY_LOGITS
+    rc = lib.frwkv_sm100_wkv7_prefill(
+        d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, pool.data_ptr(),
+        *(d[n].data_ptr() for n in TOKEN_NAMES), 0, y.data_ptr(), y32.data_ptr(), n_seq, total, heads, io, mode,
+        float(case["scale"]), 0, _lib.PREFILL_CHUNK_TC, 0, 0, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    return y.cpu(), y32.cpu(), pool.cpu(), err
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A tcgen05.commit that never comes: the waiting warps give up after about a second, the CTA raises the error
+    flag and leaves in order (every warp, the MMA-issuing one included), and the device stays usable for the next
+    call.  The commit is left out by a hook that exists only in the test build of the library
+    (tests/lib/libfrwkv_sm100_testhooks.so, the same sources with -DFRWKV_TEST_HOOKS); no GPU fault is involved,
+    the wait simply runs out."""
+    from conftest import load_testhooks
+
+    hooks = load_testhooks()
     case = _random_case((96, 40), 2, torch.bfloat16, seed=31)
-    monkeypatch.setenv("FRWKV_TEST_SKIP_COMMIT", "1")
-    _, _, _, err = _run_tc(case)
-    assert int(err.item()) == 1
-    monkeypatch.delenv("FRWKV_TEST_SKIP_COMMIT")
+    hooks.frwkv_sm100_test_skip_commit(1)
+    try:
+        _, _, _, err = _run_tc_c_abi(hooks, case)
+    finally:
+        hooks.frwkv_sm100_test_skip_commit(-1)
+    assert int(err.item()) & 1 == 1
+    _check(case, *_run_tc_c_abi(hooks, case))
     _check(case, *_run_tc(case))
+
+
+def test_decay_product_out_of_range_raises_the_error_flag():
+    """Retention mode accepts any rho, but the chunk kernel divides by the product of rho over a chunk: a caller whose
+    retentions are far below what RWKV-7 can produce (rho >= 0.545) gets bit 1 of the error flag, not a silent
+    inf/NaN; the same batch through the recurrence kernel is exact."""
+    case = _random_case((64,), 2, torch.bfloat16, seed=77)
+    case["decay_logits"] = torch.full_like(case["decay_logits"], 0.05)  # 0.05^32 is far below 2^-120
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _run_op(case, op="prefill", strategy="chunk_tc", error_flag=err)
+    assert int(err.item()) & 2 == 2
+    y, y32, pool = _run_op(case, op="prefill", strategy="recurrent")
+    y_ref, pool_ref = _oracle(case, f64=True)
+    assert max_err_over_rms(pool, pool_ref) <= 1e-5
 
 
 @pytest.mark.parametrize("seed", range(32))
@@ -282,3 +327,103 @@ def test_random_shapes_against_the_oracle(seed):
     _check(case, *_run_tc(case))
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
     _check(case, *_run_op(case, op="prefill", strategy="auto", error_flag=err), err)
+
+
+def _workload_case(wl):
+    t = wl.tensors
+    return {"r": t["r"], "decay_logits": t["w"], "k": t["k"], "v": t["v"], "a": t["a"], "b": t["b"],
+            "cu_seqlens": t["cu_seqlens"], "state_indices": t["state_indices"], "state_pool": t["state_pool"],
+            "decay_bias": None, "scale": 1.0, "decay_mode": "retention"}
+
+
+def test_retention_mode_8192_tokens_against_the_c_oracle():
+    """One sequence of 8192 tokens (the row length of the 7B-width prefill workload), two heads, retention mode,
+    through the default strategy: 256 chunks of state carry against the float64 token loop."""
+    from flashrwkv2_b200.workloads import make_workload
+
+    case = _workload_case(make_workload("c4_prefill", n_seq=1, heads=2))
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y, y32, pool = _run_op(case, op="prefill", strategy="auto", error_flag=err)
+    _check(case, y, y32, pool, err, gate=TIGHT)
+
+
+def test_ragged_workload_exact_lengths_one_head():
+    """The 64 sequence lengths of the ragged prefill workload (1 .. 8192 tokens, about 300 k rows), one head,
+    retention mode, default strategy (rows under 16 tokens take the recurrence kernel in the same call)."""
+    from flashrwkv2_b200.workloads import make_workload
+
+    wl = make_workload("c3", heads=1)
+    assert wl.n_seq == 64 and wl.total_tokens > 200_000
+    case = _workload_case(wl)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y, y32, pool = _run_op(case, op="prefill", strategy="auto", error_flag=err)
+    _check(case, y, y32, pool, err, gate=TIGHT)
+
+
+def test_prefill_operator_under_cuda_graph_capture():
+    """The prefill operator (length ranking, recurrence for short rows, chunk kernel; tensor maps encoded on the
+    host) captured in a CUDA graph with a capacity ticket, replayed after the metadata was rewritten in place, and
+    compared with the oracle (shaped after rwkv-rs/FlashRWKV2 tests/tmix/wkv7/test.py:239-373)."""
+    import flashrwkv2_b200.tmix.wkv7 as ops
+
+    lengths_a, lengths_b = (40, 70, 3), (100, 13)
+    cap_tok, cap_seq, heads, n_slots = 128, 4, 2, 5
+    case = _random_case((cap_tok,), heads, torch.bfloat16, seed=91, pool_slots=n_slots)
+    tokens = tuple(case[n].to(DEV) for n in TOKEN_NAMES)
+    initial = case["state_pool"].to(DEV)
+    state = initial.clone()
+    cu = torch.full((cap_seq + 1,), -1, dtype=torch.int32, device=DEV)
+    slots = torch.full((cap_seq,), 99, dtype=torch.int32, device=DEV)
+    n_tok = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cu[0] = 0
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.Stream()
+
+    def set_meta(lengths, use_slots):
+        ends = torch.tensor(lengths).cumsum(0).tolist()
+        cu.copy_(torch.tensor([0] + ends + [-1] * (cap_seq - len(lengths)), dtype=torch.int32))
+        slots.copy_(torch.tensor(list(use_slots) + [99] * (cap_seq - len(lengths)), dtype=torch.int32))
+        n_tok.fill_(ends[-1])
+        n_seq.fill_(len(lengths))
+
+    def run(pool):
+        ticket = ops.prepare_tmix_wkv7_recurrent_metadata(
+            cu, slots, state_pool_size=n_slots, token_capacity=cap_tok, sequence_capacity=cap_seq,
+            max_seqlen_capacity=cap_tok, num_active_tokens=n_tok, num_active_sequences=n_seq)
+        return ops.infer_tmix_wkv7_prefill_fp32io16_forward_varlen(
+            *tokens, state_pool=pool, cu_seqlens=cu, state_indices=slots, validated_metadata=ticket,
+            decay_mode="retention", error_flag=err)
+
+    def expect(lengths, use_slots):
+        total = sum(lengths)
+        ref_case = dict(case, cu_seqlens=torch.tensor([0] + torch.tensor(lengths).cumsum(0).tolist(), dtype=torch.int32),
+                        state_indices=torch.tensor(use_slots, dtype=torch.int32))
+        for n in TOKEN_NAMES:
+            ref_case[n] = case[n][:total]
+        return _oracle(ref_case, f64=True)
+
+    set_meta(lengths_a, (4, 0, 2))
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        run(state.clone())  # warm-up outside capture: kernel attributes, tensor-map cache, allocator pools
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        y = run(state)
+    for lengths, use_slots in ((lengths_a, (4, 0, 2)), (lengths_b, (1, 3))):
+        state.copy_(initial)
+        set_meta(lengths, use_slots)
+        graph.replay()
+        torch.cuda.synchronize()
+        y_ref, pool_ref = expect(lengths, use_slots)
+        total = sum(lengths)
+        assert max_err_over_rms(y[:total].float().cpu(), y_ref) <= 3e-2  # bf16 rounding of y on top of the gate
+        assert relative_rmse(y[:total].cpu(), y_ref) <= 7e-3
+        touched = list(use_slots)
+        assert max_err_over_rms(state.cpu()[touched], pool_ref[touched]) <= TIGHT
+        for slot in range(n_slots):
+            if slot not in touched:
+                assert torch.equal(state[slot], initial[slot])
+        assert int(err.item()) == 0

@@ -146,22 +146,28 @@ def test_config0_fp32_inputs():
 
 
 @pytest.mark.parametrize("parts", (2, 4, 8))
-def test_decode_step_all_launch_shapes(parts, monkeypatch):
-    """T=1 rows through every column split of the kernel, via the C ABI directly."""
+def test_decode_step_all_launch_shapes(parts):
+    """T=1 rows through every column split of the kernel, via the C ABI of the library's test build (the split
+    is forced by a setter that only that build has)."""
+    from conftest import load_testhooks
+
     from flashrwkv2_b200 import _lib
 
-    monkeypatch.setenv("FRWKV_RECURRENT_PARTS", str(parts))
     case = _random_case((1,) * 24, 3, torch.bfloat16, seed=parts)
     d = _to_dev(case)
     pool = d["state_pool"].clone()
     y = torch.empty_like(d["v"])
     y32 = torch.empty(d["v"].shape, dtype=torch.float32, device=DEV)
-    lib = _lib.load()
-    rc = lib.frwkv_sm100_wkv7_recurrent(
-        d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, pool.data_ptr(),
-        *(d[n].data_ptr() for n in TOKEN_NAMES), 0, y.data_ptr(), y32.data_ptr(), 24, 24, 3,
-        _lib.IO_BF16, _lib.DECAY_RETENTION, 1.0, 1, torch.cuda.current_stream().cuda_stream)
-    assert rc == 0, _lib.last_error()
+    lib = load_testhooks()
+    lib.frwkv_sm100_test_recurrent_parts(parts)
+    try:
+        rc = lib.frwkv_sm100_wkv7_recurrent(
+            d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, pool.data_ptr(),
+            *(d[n].data_ptr() for n in TOKEN_NAMES), 0, y.data_ptr(), y32.data_ptr(), 24, 24, 3,
+            _lib.IO_BF16, _lib.DECAY_RETENTION, 1.0, 1, torch.cuda.current_stream().cuda_stream)
+    finally:
+        lib.frwkv_sm100_test_recurrent_parts(0)
+    assert rc == 0
     torch.cuda.synchronize()
     _assert_parity(case, y.cpu(), y32.cpu(), pool.cpu())
 
