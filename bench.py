@@ -52,6 +52,7 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "WKV7 tokens/s & % roofline (decode HBM, prefill TC) at 1/2/4/8 B200"
 ALGO_BYTES_DECODE_PAIR = 16384 + 16384 + 6 * 128 + 128  # state in + out, six bf16 rows, one bf16 y row
+ALGO_BYTES_DECODE_FP16_STATE_PAIR = 8192 + 8192 + 6 * 128 + 128  # the fp16-state contract: half the state bytes
 ALGO_FLOP_PREFILL_TOKEN_HEAD = 98304  # 12 GEMMs of 64^3 per 64 rows
 ALGO_BYTES_PREFILL_TOKEN_HEAD = 7 * 128
 ALGO_BYTES_PREFILL_PAIR = 32768
@@ -338,6 +339,50 @@ def measure(name, args, rank, local_rank, world, *, with_e2e=True, steps=None, w
     return block
 
 
+def measure_fp16_state_decode(args, local_rank):
+    """The fp16-state decode contract on the 7B-width decode batch (2048 sequences, H=64, fp16 tokens, decay
+    logits, fp16 state pool): same kernel, half the state traffic.  One GPU, device-resident."""
+    import torch
+
+    from flashrwkv2_b200 import _lib, dist as fdist
+    from flashrwkv2_b200.workloads import make_workload
+
+    device = torch.device("cuda", local_rank)
+    lib = _lib.load()
+    peaks, peak_kind = load_peaks()
+    wl = make_workload("c4_decode", device=device)
+    t = wl.tensors
+    n_seq, heads, tokens = wl.n_seq, wl.heads, wl.total_tokens
+    tok = {n: t[n].half() for n in "rkvab"}
+    sig = (-torch.log(t["w"].float()) / 0.6065306597126334).clamp(1e-4, 1 - 1e-4)
+    tok["w"] = torch.log(sig / (1 - sig)).half()  # the decay logits whose retention is w
+    pools = [t["state_pool"].half() for _ in range(2)]  # 2 x 1 GiB in rotation
+    elapsed = torch.zeros(n_seq, dtype=torch.int32, device=device)
+    y = torch.empty_like(tok["v"])
+    stream = torch.cuda.current_stream().cuda_stream
+    sampler = ClockSampler(local_rank).start()
+
+    def step(i):
+        rc = lib.frwkv_sm100_wkv7_recurrent_fp16_state(
+            t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, elapsed.data_ptr(), pools[i % 2].data_ptr(),
+            tok["r"].data_ptr(), tok["w"].data_ptr(), tok["k"].data_ptr(), tok["v"].data_ptr(), tok["a"].data_ptr(),
+            tok["b"].data_ptr(), 0, y.data_ptr(), n_seq, tokens, heads, _lib.DECAY_LOGITS, 1.0, 1, stream)
+        if rc:
+            raise RuntimeError(_lib.last_error())
+
+    ms_per_step, repeats = _timed_region(step, args.steps, args.warmup, fdist)
+    algo = n_seq * heads * ALGO_BYTES_DECODE_FP16_STATE_PAIR
+    achieved = algo / (ms_per_step * 1e-3) / 1e9
+    return {"workload": "c4_decode shapes, fp16 tokens (decay logits), fp16 state pool, elapsed-phase dither",
+            "value": round(tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms_per_step, 6),
+            "steps": args.steps, "repeats": repeats, "gpu_launches": 2 * args.steps * repeats,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo,
+                         "kernel": "wkv7_recurrent_stream_kernel<half state> + advance_elapsed_kernel"},
+            "clocks": sampler.stop()}
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
 
@@ -373,6 +418,11 @@ def run_ours(args, rank, local_rank, world):
             except RuntimeError as error:  # reported, not hidden
                 extras[extra] = {"error": str(error)}
             torch.cuda.empty_cache()
+        try:
+            extras["c4_decode_fp16_state"] = measure_fp16_state_decode(args, local_rank)
+        except RuntimeError as error:
+            extras["c4_decode_fp16_state"] = {"error": str(error)}
+        torch.cuda.empty_cache()
         try:
             extras["gpu_baseline"] = gpu_baseline(torch.device("cuda", local_rank))
         except Exception as error:  # a baseline that cannot load or run must not take the bench line with it

@@ -23,6 +23,7 @@ SYMBOLS = (
     "frwkv_sm100_wkv7_validate_metadata",
     "frwkv_sm100_wkv7_validate_metadata_static",
     "frwkv_sm100_wkv7_recurrent",
+    "frwkv_sm100_wkv7_recurrent_fp16_state",
     "frwkv_sm100_wkv7_prefill",
     "frwkv_sm100_wkv7_prefill_workspace_bytes",
 )
@@ -62,6 +63,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_validate_metadata_static.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]
     lib.frwkv_sm100_wkv7_recurrent.restype = ci
     lib.frwkv_sm100_wkv7_recurrent.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, vp]
+    lib.frwkv_sm100_wkv7_recurrent_fp16_state.restype = ci
+    lib.frwkv_sm100_wkv7_recurrent_fp16_state.argtypes = [vp] * 13 + [ci, ci, ci, ci, cf, ci, vp]
     lib.frwkv_sm100_wkv7_prefill.restype = ci
     lib.frwkv_sm100_wkv7_prefill.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     lib.frwkv_sm100_wkv7_prefill_workspace_bytes.restype = sz

@@ -342,6 +342,69 @@ void tmix_wkv7_recurrent_fp32_from_decay_logits(torch::Tensor query_start_loc, t
       static_cast<int>(meta.max_seqlen), at::cuda::getCurrentCUDAStream(state.device().index()).stream()));
 }
 
+// fp16-state contract; argument order and checks of the reference binding
+// (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cpp:44-190).
+void tmix_wkv7_recurrent_fp16_from_decay_logits(torch::Tensor query_start_loc, torch::Tensor state_indices,
+                                                torch::Tensor elapsed_state, torch::Tensor state, torch::Tensor r,
+                                                torch::Tensor decay_logits, torch::Tensor k, torch::Tensor v,
+                                                torch::Tensor a, torch::Tensor b, torch::Tensor output, double scale,
+                                                std::optional<torch::Tensor> decay_bias, TicketPtr validated_metadata,
+                                                int64_t max_seqlen) {
+  const std::pair<const torch::Tensor*, const char*> named[] = {
+      {&query_start_loc, "query_start_loc"}, {&state_indices, "state_indices"}, {&elapsed_state, "elapsed_state_pool"},
+      {&state, "state"}, {&r, "r"}, {&decay_logits, "decay_logits"}, {&k, "k"}, {&v, "v"}, {&a, "a"}, {&b, "b"},
+      {&output, "output"}};
+  for (const auto& item : named) check_cuda_contiguous(*item.first, item.second);
+  for (const auto& item : named) check_same_device(state, *item.first, item.second);
+  TORCH_CHECK(query_start_loc.scalar_type() == torch::kInt32 && state_indices.scalar_type() == torch::kInt32,
+              "query_start_loc and state_indices must be int32");
+  TORCH_CHECK(std::isfinite(scale), "scale must be finite");
+  const int64_t n = state_indices.numel();
+  TORCH_CHECK(state_indices.dim() == 1 && n > 0 && n <= 65535, "state_indices must contain 1..65535 sequences");
+  TORCH_CHECK(query_start_loc.dim() == 1 && query_start_loc.size(0) == n + 1, "query_start_loc must have shape [N+1]");
+  TORCH_CHECK(state.dim() == 4 && state.size(0) > 0 && state.size(1) > 0 && state.size(2) == state.size(3),
+              "state must have square shape [slots,H,D,D]");
+  TORCH_CHECK(state.scalar_type() == torch::kFloat16, "FP16-state state must be float16");
+  TORCH_CHECK(state.size(2) == kHeadSize, "the sm_100a backend implements head size 64 only, got ", state.size(2));
+  TORCH_CHECK(elapsed_state.scalar_type() == torch::kInt32, "elapsed_state_pool must be int32");
+  TORCH_CHECK(elapsed_state.dim() == 1 && elapsed_state.size(0) == state.size(0),
+              "elapsed_state_pool must have shape [state_pool_slots]");
+  const int64_t h = state.size(1);
+  TORCH_CHECK(r.dim() == 3 && r.size(0) > 0 && r.size(1) == h && r.size(2) == kHeadSize,
+              "r must have shape [total_tokens,H,D] matching state");
+  TORCH_CHECK(r.size(0) <= std::numeric_limits<int>::max(), "token count must fit in int32");
+  TORCH_CHECK(r.sizes() == decay_logits.sizes() && r.sizes() == k.sizes() && r.sizes() == v.sizes() &&
+                  r.sizes() == a.sizes() && r.sizes() == b.sizes() && r.sizes() == output.sizes(),
+              "r,decay_logits,k,v,a,b,output shape mismatch");
+  for (const torch::Tensor* t : {&r, &decay_logits, &k, &v, &a, &b, &output})
+    TORCH_CHECK(t->scalar_type() == torch::kFloat16, "FP16-state token tensors must be float16");
+  if (decay_bias.has_value()) {
+    check_cuda_contiguous(*decay_bias, "decay_bias");
+    check_same_device(state, *decay_bias, "decay_bias");
+    TORCH_CHECK(decay_bias->scalar_type() == torch::kFloat16 &&
+                    ((decay_bias->dim() == 1 && decay_bias->numel() == h * kHeadSize) ||
+                     (decay_bias->dim() == 2 && decay_bias->size(0) == h && decay_bias->size(1) == kHeadSize)),
+                "decay_bias must be float16 with shape [H*D] or [H,D]");
+  }
+  Resolved meta;
+  if (validated_metadata) {
+    validated_metadata->check_compatible(query_start_loc, state_indices, r.size(0), state.size(0), max_seqlen);
+    meta = Resolved{validated_metadata->cu_snapshot(), validated_metadata->slots_snapshot(),
+                    validated_metadata->status(), validated_metadata->max_seqlen(), torch::Tensor()};
+  } else {
+    auto prepared = launch_validation(query_start_loc, state_indices, torch::Tensor(), torch::Tensor(), r.size(0),
+                                      state_indices.numel(), state.size(0), r.size(0), true);
+    meta = Resolved{prepared.cu, prepared.slots, prepared.status, max_seqlen, prepared.workspace};
+  }
+  const c10::cuda::CUDAGuard guard(state.device());
+  check_abi(frwkv_sm100_wkv7_recurrent_fp16_state(
+      meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), elapsed_state.data_ptr<int>(),
+      state.data_ptr(), r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+      decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, output.data_ptr(), static_cast<int>(n),
+      static_cast<int>(r.size(0)), static_cast<int>(h), FRWKV_DECAY_LOGITS, static_cast<float>(scale),
+      static_cast<int>(meta.max_seqlen), at::cuda::getCurrentCUDAStream(state.device().index()).stream()));
+}
+
 void tmix_wkv7_prefill_fp32(torch::Tensor query_start_loc, torch::Tensor state_indices, torch::Tensor state,
                             torch::Tensor r, torch::Tensor decay_logits, torch::Tensor k, torch::Tensor v,
                             torch::Tensor a, torch::Tensor b, torch::Tensor output, double scale,
@@ -446,6 +509,12 @@ void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_& module) {
              py::arg("v"), py::arg("a"), py::arg("b"), py::arg("output"), py::arg("scale"),
              py::arg("decay_bias") = py::none(), py::arg("validated_metadata") = py::none(),
              py::arg("max_seqlen") = -1, py::arg("decay_mode") = "logits", py::arg("output_f32") = py::none());
+  module.def("tmix_wkv7_recurrent_fp16_from_decay_logits", &tmix_wkv7_recurrent_fp16_from_decay_logits,
+             "WKV7 recurrence with an fp16 state pool, delta decay and elapsed-phase dither, in place",
+             py::arg("query_start_loc"), py::arg("state_indices"), py::arg("elapsed_state_pool"), py::arg("state"),
+             py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"),
+             py::arg("output"), py::arg("scale"), py::arg("decay_bias") = py::none(),
+             py::arg("validated_metadata") = py::none(), py::arg("max_seqlen") = -1);
   module.def("tmix_wkv7_prefill_fp32", &tmix_wkv7_prefill_fp32,
              "WKV7 chunked prefill taking cu_seqlens directly, fp32 state in place", py::arg("query_start_loc"),
              py::arg("state_indices"), py::arg("state"), py::arg("r"), py::arg("decay_logits"), py::arg("k"),

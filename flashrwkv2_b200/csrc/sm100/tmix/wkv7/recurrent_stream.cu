@@ -14,6 +14,12 @@
 //
 // Per token (tests/tmix/wkv7/test.py:66-83 of the reference):
 //   sa = a^T S;  S = diag(rho) S + b sa + k v^T;  y = scale * r^T S.
+//
+// The same kernel serves the reference's fp16-state decode contract (state pool in fp16, fp16 tokens;
+// csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:244-340, oracle tests/tmix/wkv7/test.py:88-149):
+//   delta = fp16(rho - 1 + dither(phase)),  phase = elapsed[slot] + head*64 + key + token offset,
+//   S = fp16(S + S*delta + b sa + k v^T) evaluated in fp32,  y = fp16(scale * r^T S) from the rounded state.
+// A key row is then 128 contiguous bytes and a lane moves 8 bytes of it per access; everything else is shared.
 #include "../../common.cuh"
 
 #include <cstdlib>
@@ -80,16 +86,57 @@ template <typename io_t> struct Quad {  // 4 consecutive token-dtype values (val
   }
 };
 
+template <typename io_t> struct Pair {  // 2 consecutive token-dtype values
+  io_t vals[2];
+  __device__ __forceinline__ void load(const io_t* p) {
+    if constexpr (sizeof(io_t) == 2) {
+      *reinterpret_cast<uint32_t*>(vals) = __ldg(reinterpret_cast<const uint32_t*>(p));
+    } else {
+      *reinterpret_cast<uint2*>(vals) = __ldg(reinterpret_cast<const uint2*>(p));
+    }
+  }
+};
+
 template <typename io_t, int RPL> struct TokenRows {  // one token's operands for this lane
   RowVals<io_t, RPL> r, w, k, a, b;
+  Pair<io_t> w2;  // the two key rows whose decay this lane evaluates for its row group (see the kernel)
   Quad<io_t> v;
 };
+
+// Dither of the fp16-state update (csrc/sm120/tmix/wkv7/recurrent_decay.cuh:32-46 of the reference): a
+// multiplicative hash of the phase, scaled to +-2^-10, added to rho - 1 before it is rounded to fp16.
+__device__ __forceinline__ float fp16_state_dither(int phase) {
+  const uint32_t bits = 2654435769u * static_cast<uint32_t>(phase);
+  return 4.547473508864641e-13f * static_cast<float>(static_cast<int32_t>(bits));
+}
+__device__ __forceinline__ float round_to_half(float x) { return __half2float(__float2half_rn(x)); }
+
+// four consecutive state values of one key row
+template <typename state_t> __device__ __forceinline__ float4 load_state4(const state_t* p);
+template <> __device__ __forceinline__ float4 load_state4<float>(const float* p) {
+  return __ldcs(reinterpret_cast<const float4*>(p));
+}
+template <> __device__ __forceinline__ float4 load_state4<__half>(const __half* p) {
+  const uint2 q = __ldcs(reinterpret_cast<const uint2*>(p));
+  const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+  const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store_state4(float* p, const float4& v) { __stcs(reinterpret_cast<float4*>(p), v); }
+__device__ __forceinline__ void store_state4(__half* p, const float4& v) {
+  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  uint2 q;
+  q.x = *reinterpret_cast<const uint32_t*>(&lo);
+  q.y = *reinterpret_cast<const uint32_t*>(&hi);
+  __stcs(reinterpret_cast<uint2*>(p), q);
+}
 
 struct RecurrentParams {
   const int* cu;
   const int* slots;
   const int* status;
-  float* pool;
+  void* pool;           // fp32 pool, or fp16 pool of the fp16-state contract
+  const int* elapsed;   // fp16-state contract: per-slot phase counter (read here, advanced by advance_elapsed_kernel)
   const void *r, *w, *k, *v, *a, *b, *bias;
   void* y;
   float* y_f32;
@@ -98,8 +145,19 @@ struct RecurrentParams {
   int len_below;  // > 0: only sequences shorter than this (the rest belongs to another kernel of the same call)
 };
 
-template <typename io_t, int PARTS, bool LOGITS, bool PREFETCH>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kernel(const RecurrentParams p) {
+// Resident CTAs per SM asked of the compiler.  The one-token kernels are sized by bytes in flight: with an fp32
+// state 4 CTAs (128 registers) already saturate HBM; a warp of the fp16-state kernel carries half the bytes, so it
+// runs with 5 (96 registers, a few spilled words).  0 = no request (multi-token variants).  A request of 1 is not
+// the same as none: it makes the compiler spend 190 registers and costs a third of the bandwidth.
+#ifndef FRWKV_HALF_STATE_MIN_CTAS
+#define FRWKV_HALF_STATE_MIN_CTAS 5
+#endif
+template <typename io_t, typename state_t, int PARTS, bool LOGITS, bool PREFETCH>
+__global__ void __launch_bounds__(kWarpsPerCta * 32,
+                                  (PREFETCH || sizeof(io_t) == 4)
+                                      ? 0 : (std::is_same<state_t, __half>::value ? FRWKV_HALF_STATE_MIN_CTAS : 4))
+wkv7_recurrent_stream_kernel(const RecurrentParams p) {
+  constexpr bool kHalfState = std::is_same<state_t, __half>::value;
   constexpr int COLS = kHeadDim / PARTS;   // value columns of this warp
   constexpr int LPR = COLS / 4;            // lanes per key row
   constexpr int GROUPS = 32 / LPR;         // key-row groups in a warp
@@ -135,11 +193,11 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
   const int col = part * COLS + (lane % LPR) * 4;
   const int row0 = group * RPL;
 
-  float* sbase = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim) +
-                 static_cast<size_t>(row0) * kHeadDim + col;
+  state_t* sbase = static_cast<state_t*>(p.pool) + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim) +
+                   static_cast<size_t>(row0) * kHeadDim + col;
   float4 S[RPL];
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) S[i] = __ldcs(reinterpret_cast<const float4*>(sbase + i * kHeadDim));
+  for (int i = 0; i < RPL; ++i) S[i] = load_state4<state_t>(sbase + i * kHeadDim);
 
   const io_t* rp = static_cast<const io_t*>(p.r);
   const io_t* wp = static_cast<const io_t*>(p.w);
@@ -149,14 +207,27 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
   const io_t* bp = static_cast<const io_t*>(p.b);
   io_t* yp = static_cast<io_t*>(p.y);
 
-  RowVals<io_t, RPL> bias;
+  // Decay per key row.  In retention mode with an fp32 state the lane simply reads w for its rows.  Otherwise the
+  // decay is work per row (two exp2 and a divide for logits; dither, delta and a rounding for the fp16 state) that
+  // the LPR lanes of a row group would repeat: every lane does it for two of the group's rows (RPL = 2 * LPR for
+  // every column split) and the values are handed round with shuffles.
+  constexpr bool kSharedDecay = LOGITS || kHalfState;
+  static_assert(RPL == 2 * LPR, "two decay rows per lane");
+  const int my_rows = row0 + 2 * (lane % LPR);
+  Pair<io_t> bias2;
   const bool has_bias = LOGITS && p.bias != nullptr;
-  if (has_bias) bias.load(static_cast<const io_t*>(p.bias) + head * kHeadDim + row0);
+  if (has_bias) bias2.load(static_cast<const io_t*>(p.bias) + head * kHeadDim + my_rows);
+  int phase0 = 0;  // fp16 state: dither phase of this lane's first decay row at the sequence's first token
+  if constexpr (kHalfState) phase0 = p.elapsed[slot] + head * kHeadDim + my_rows - t_lo;
 
   auto fetch = [&](TokenRows<io_t, RPL>& dst, int t) {
     const size_t row = (static_cast<size_t>(t) * p.heads + head) * kHeadDim;
     dst.a.load(ap + row + row0);
-    dst.w.load(wp + row + row0);
+    if constexpr (kSharedDecay) {
+      dst.w2.load(wp + row + my_rows);
+    } else {
+      dst.w.load(wp + row + row0);
+    }
     dst.b.load(bp + row + row0);
     dst.k.load(kp + row + row0);
     dst.r.load(rp + row + row0);
@@ -191,15 +262,47 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
     const float4 v4 = make_float4(to_f32(cur.v.vals[0]), to_f32(cur.v.vals[1]), to_f32(cur.v.vals[2]),
                                   to_f32(cur.v.vals[3]));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float mine[2] = {0.f, 0.f};  // rho (fp32 state) or delta (fp16 state) of this lane's two decay rows
+    if constexpr (kSharedDecay) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float x = to_f32(cur.w2.vals[e]);
+        if constexpr (LOGITS) {
+          if (has_bias) x += to_f32(bias2.vals[e]);
+#if defined(FRWKV_EXP_IDENTITY)
+          x = 0.9f;
+#elif defined(FRWKV_FAST_DECAY)
+          x = sizeof(io_t) == 2 ? retention_from_logit_fast(x) : retention_from_logit(x);
+#else
+          x = retention_from_logit(x);
+#endif
+        }
+        if constexpr (kHalfState) x = round_to_half(x - 1.0f + fp16_state_dither(phase0 + e + t));
+        mine[e] = x;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < RPL; ++i) {
-      float fw = cur.w.get(i);
-      if constexpr (LOGITS) fw = retention_from_logit(has_bias ? fw + bias.get(i) : fw);
+      float fw;
+      if constexpr (kSharedDecay) {
+        fw = __shfl_sync(0xffffffffu, mine[i & 1], group * LPR + (i >> 1));
+      } else {
+        fw = cur.w.get(i);
+      }
       const float fb = cur.b.get(i), fk = cur.k.get(i), fr = cur.r.get(i);
-      S[i].x = fmaf(fw, S[i].x, fmaf(fb, sa.x, fk * v4.x));
-      S[i].y = fmaf(fw, S[i].y, fmaf(fb, sa.y, fk * v4.y));
-      S[i].z = fmaf(fw, S[i].z, fmaf(fb, sa.z, fk * v4.z));
-      S[i].w = fmaf(fw, S[i].w, fmaf(fb, sa.w, fk * v4.w));
+      if constexpr (kHalfState) {
+        // S + S*delta + b*sa + k*v in fp32, then rounded to the stored precision; y reads the rounded state
+        const float delta = fw;
+        S[i].x = round_to_half(fmaf(fk, v4.x, fmaf(fb, sa.x, fmaf(S[i].x, delta, S[i].x))));
+        S[i].y = round_to_half(fmaf(fk, v4.y, fmaf(fb, sa.y, fmaf(S[i].y, delta, S[i].y))));
+        S[i].z = round_to_half(fmaf(fk, v4.z, fmaf(fb, sa.z, fmaf(S[i].z, delta, S[i].z))));
+        S[i].w = round_to_half(fmaf(fk, v4.w, fmaf(fb, sa.w, fmaf(S[i].w, delta, S[i].w))));
+      } else {
+        S[i].x = fmaf(fw, S[i].x, fmaf(fb, sa.x, fk * v4.x));
+        S[i].y = fmaf(fw, S[i].y, fmaf(fb, sa.y, fk * v4.y));
+        S[i].z = fmaf(fw, S[i].z, fmaf(fb, sa.z, fk * v4.z));
+        S[i].w = fmaf(fw, S[i].w, fmaf(fb, sa.w, fk * v4.w));
+      }
       acc.x = fmaf(fr, S[i].x, acc.x);
       acc.y = fmaf(fr, S[i].y, acc.y);
       acc.z = fmaf(fr, S[i].z, acc.z);
@@ -225,7 +328,20 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) wkv7_recurrent_stream_kerne
     }
   }
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) __stcs(reinterpret_cast<float4*>(sbase + i * kHeadDim), S[i]);
+  for (int i = 0; i < RPL; ++i) store_state4(sbase + i * kHeadDim, S[i]);
+}
+
+// fp16-state contract: after the recurrence every active sequence's phase counter moves on by its token count
+// (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:57-75 of the reference).  A separate launch: the
+// recurrence's CTAs of all heads read the counter, so nobody may change it while they run.  Fail-closed like the
+// recurrence: invalid metadata leaves every counter untouched.
+__global__ void advance_elapsed_kernel(const int* __restrict__ cu, const int* __restrict__ slots,
+                                       const int* __restrict__ status, int* __restrict__ elapsed, int n_seq) {
+  if (status != nullptr && status[0] != 0) return;
+  const int active = status != nullptr ? status[2] : n_seq;
+  const int seq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (seq >= n_seq || seq >= active) return;
+  elapsed[slots[seq]] += cu[seq + 1] - cu[seq];
 }
 
 // Tuning hooks, read from the environment once per process (not on every launch):
@@ -251,7 +367,7 @@ int& test_recurrent_parts() {  // test build only: column split forced by the ne
 }
 #endif
 
-template <typename io_t, int PARTS, bool PREFETCH>
+template <typename io_t, typename state_t, int PARTS, bool PREFETCH>
 int launch(const RecurrentParams& p, bool logits, cudaStream_t stream) {
   const long long warps = static_cast<long long>(p.n_seq) * p.heads * PARTS;
   const long long ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -268,23 +384,37 @@ int launch(const RecurrentParams& p, bool logits, cudaStream_t stream) {
   attribute[0].val.programmaticStreamSerializationAllowed = (!PREFETCH && pdl_enabled()) ? 1 : 0;
   config.attrs = attribute;
   config.numAttrs = 1;
-  auto kernel = logits ? wkv7_recurrent_stream_kernel<io_t, PARTS, true, PREFETCH>
-                       : wkv7_recurrent_stream_kernel<io_t, PARTS, false, PREFETCH>;
+  auto kernel = logits ? wkv7_recurrent_stream_kernel<io_t, state_t, PARTS, true, PREFETCH>
+                       : wkv7_recurrent_stream_kernel<io_t, state_t, PARTS, false, PREFETCH>;
   const cudaError_t err = cudaLaunchKernelEx(&config, kernel, p);
   if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent_stream_kernel: %s", cudaGetErrorString(err));
   return check_launch("wkv7_recurrent_stream_kernel");
 }
 
-template <typename io_t>
+template <typename io_t, typename state_t = float>
 int dispatch_parts(const RecurrentParams& p, bool logits, int parts, bool prefetch, cudaStream_t stream) {
   if (!prefetch) {
-    if (parts == 2) return launch<io_t, 2, false>(p, logits, stream);
-    if (parts == 4) return launch<io_t, 4, false>(p, logits, stream);
-    return launch<io_t, 8, false>(p, logits, stream);
+    if (parts == 2) return launch<io_t, state_t, 2, false>(p, logits, stream);
+    if (parts == 4) return launch<io_t, state_t, 4, false>(p, logits, stream);
+    return launch<io_t, state_t, 8, false>(p, logits, stream);
   }
-  if (parts == 2) return launch<io_t, 2, true>(p, logits, stream);
-  if (parts == 4) return launch<io_t, 4, true>(p, logits, stream);
-  return launch<io_t, 8, true>(p, logits, stream);
+  if (parts == 2) return launch<io_t, state_t, 2, true>(p, logits, stream);
+  if (parts == 4) return launch<io_t, state_t, 4, true>(p, logits, stream);
+  return launch<io_t, state_t, 8, true>(p, logits, stream);
+}
+
+// column split: see launch_recurrent_stream
+int choose_parts(int n_seq, int heads, int max_seqlen, int parts_override) {
+  int parts = 2;
+  const long long pairs = static_cast<long long>(n_seq) * heads;
+  if (max_seqlen <= 0 || max_seqlen > 2) parts = 4;
+  if (max_seqlen <= 0 || max_seqlen > 64 || pairs < 148LL * 4) parts = 8;
+  if (parts_override == 0) parts_override = parts_from_environment();
+#ifdef FRWKV_TEST_HOOKS
+  if (test_recurrent_parts() != 0) parts_override = test_recurrent_parts();
+#endif
+  if (parts_override == 2 || parts_override == 4 || parts_override == 8) parts = parts_override;
+  return parts;
 }
 
 }  // namespace
@@ -322,21 +452,13 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
                             int max_seqlen, int parts_override, int len_below, cudaStream_t stream) {
-  RecurrentParams p{cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads, scale,
-                    len_below};
+  RecurrentParams p{cu, slots, status, pool, nullptr, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
+                    scale, len_below};
   // Launch shape.  Decode (one token per row): the state is loaded, used once and stored,
   // so all that matters is bytes in flight; two column parts per pair keep every access a
   // full 128-byte line.  Long rows are a latency-bound token loop: thinner warps (more of
   // them, fewer rows per lane, next token prefetched) shorten the per-token chain.
-  int parts = 2;
-  const long long pairs = static_cast<long long>(n_seq) * heads;
-  if (max_seqlen <= 0 || max_seqlen > 2) parts = 4;
-  if (max_seqlen <= 0 || max_seqlen > 64 || pairs < 148LL * 4) parts = 8;
-  if (parts_override == 0) parts_override = parts_from_environment();
-#ifdef FRWKV_TEST_HOOKS
-  if (test_recurrent_parts() != 0) parts_override = test_recurrent_parts();
-#endif
-  if (parts_override == 2 || parts_override == 4 || parts_override == 8) parts = parts_override;
+  const int parts = choose_parts(n_seq, heads, max_seqlen, parts_override);
   const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
   switch (io_dtype) {
@@ -346,7 +468,37 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
   }
 }
 
+int launch_recurrent_fp16_state(const int32_t* cu, const int32_t* slots, const int32_t* status, int32_t* elapsed,
+                                void* pool, const void* r, const void* w, const void* k, const void* v,
+                                const void* a, const void* b, const void* bias, void* y, int n_seq, int total_tokens,
+                                int heads, int decay_mode, float scale, int max_seqlen, cudaStream_t stream) {
+  RecurrentParams p{cu, slots, status, pool, elapsed, r, w, k, v, a, b, bias, y, nullptr, n_seq, total_tokens, heads,
+                    scale, 0};
+  const int parts = choose_parts(n_seq, heads, max_seqlen, 0);
+  const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
+  const int rc = dispatch_parts<__half, __half>(p, decay_mode == FRWKV_DECAY_LOGITS, parts, prefetch, stream);
+  if (rc != FRWKV_OK) return rc;
+  advance_elapsed_kernel<<<(n_seq + 255) / 256, 256, 0, stream>>>(cu, slots, status, elapsed, n_seq);
+  return check_launch("advance_elapsed_kernel");
+}
+
 }  // namespace frwkv
+
+extern "C" int frwkv_sm100_wkv7_recurrent_fp16_state(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, int32_t* elapsed_pool,
+    void* state_pool_f16, const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* decay_bias, void* y, int n_seq, int total_tokens, int heads, int decay_mode, float scale,
+    int max_seqlen, void* stream) {
+  using namespace frwkv;
+  if (elapsed_pool == nullptr) return fail(FRWKV_ERR_ARGUMENT, "wkv7_recurrent_fp16_state: elapsed_pool must be non-null");
+  int rc = check_wkv7_arguments("wkv7_recurrent_fp16_state", cu_seqlens, slots, static_cast<float*>(state_pool_f16), r, w,
+                                k, v, a, b, decay_bias, y, nullptr, n_seq, total_tokens, heads, FRWKV_IO_FP16,
+                                decay_mode, scale);
+  if (rc != FRWKV_OK) return rc;
+  return launch_recurrent_fp16_state(cu_seqlens, slots, status, elapsed_pool, state_pool_f16, r, w, k, v, a, b,
+                                     decay_bias, y, n_seq, total_tokens, heads, decay_mode, scale, max_seqlen,
+                                     static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int frwkv_sm100_wkv7_recurrent(
     const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,

@@ -118,10 +118,50 @@ def infer_tmix_wkv7_prefill_fp32io16_forward_varlen(
                    extra=(decay_mode, strategy, output_f32, error_flag))
 
 
+def infer_tmix_wkv7_recurrent_fp16_forward_varlen(
+        r: torch.Tensor, decay_logits: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
+        b: torch.Tensor, *, state_pool: torch.Tensor, elapsed_state_pool: torch.Tensor, cu_seqlens: torch.Tensor,
+        state_indices: torch.Tensor, scale: float = 1.0, decay_bias: torch.Tensor | None = None,
+        max_seqlen: int | None = None, validated_metadata: object | None = None) -> torch.Tensor:
+    """Packed recurrence with an fp16 state pool (half the state traffic of the fp32 contract): fp16 tokens, decay
+    applied as ``state + state * delta`` with a dithered fp16 delta, state rounded to fp16 after every token, in
+    place on ``state_pool``; ``elapsed_state_pool`` (int32 ``[slots]``) supplies the dither phase and advances by
+    each sequence's token count.  Reference: flashrwkv2/tmix/wkv7/__init__.py:259-318 (same signature, checks
+    and error types)."""
+    tokens = (r, decay_logits, k, v, a, b)
+    check.packed_tokens(tokens)
+    check.tensor(state_pool, "state_pool")
+    check.need(state_pool.is_contiguous(), ValueError, "state_pool must be contiguous")
+    check.need(state_pool.dtype == torch.float16, TypeError, "FP16-state state_pool must have dtype float16")
+    check.tensor(elapsed_state_pool, "elapsed_state_pool")
+    check.need(elapsed_state_pool.dtype == torch.int32, TypeError, "elapsed_state_pool must have dtype torch.int32")
+    check.need(elapsed_state_pool.is_cuda and elapsed_state_pool.is_contiguous(), ValueError,
+               "elapsed_state_pool must be contiguous CUDA int32")
+    check.need(elapsed_state_pool.device == state_pool.device, ValueError,
+               "elapsed_state_pool must share state_pool's device")
+    check.need(elapsed_state_pool.ndim == 1 and elapsed_state_pool.shape[0] == state_pool.shape[0], ValueError,
+               "elapsed_state_pool must have shape [state_pool_slots]")
+    check.metadata(cu_seqlens, state_indices)
+    if max_seqlen is not None:
+        check.positive_int(max_seqlen, "max_seqlen")
+    launch_max_seqlen = -1 if max_seqlen is None else int(max_seqlen)
+    ticket = validated_metadata
+    if ticket is None:
+        ticket = prepare_tmix_wkv7_recurrent_metadata(
+            cu_seqlens, state_indices, total_tokens=r.shape[0], state_pool_size=state_pool.shape[0],
+            max_seqlen=max_seqlen)
+    y = torch.empty_like(v)
+    _extension().tmix_wkv7_recurrent_fp16_from_decay_logits(
+        cu_seqlens, state_indices, elapsed_state_pool, state_pool, *tokens, y, float(scale), decay_bias, ticket,
+        launch_max_seqlen)
+    return y
+
+
 from .rl_infctx import rl_infctx_tmix_wkv7_chunk_fp32io16  # noqa: E402
 
 __all__ = [
     "infer_tmix_wkv7_prefill_fp32io16_forward_varlen",
+    "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",
     "prepare_tmix_wkv7_recurrent_metadata",
     "rl_infctx_tmix_wkv7_chunk_fp32io16",

@@ -35,9 +35,10 @@ enum { FRWKV_IO_BF16 = 0, FRWKV_IO_FP16 = 1, FRWKV_IO_FP32 = 2 };
  * rho = exp(-exp(-1/2) * sigmoid(w + bias)), csrc/sm120/tmix/wkv7/recurrent_decay.cuh:18-23)
  * or the retention rho itself (how the benchmark workloads are specified).
  * RWKV-7 retentions lie in [exp(-exp(-1/2)), 1] = [0.545, 1], which is what the logits form can produce.  The chunked
- * prefill kernels divide by the running product of rho over one chunk (32 or 64 rows), so in retention mode they need
- * rho >= 0.26 (64-row chunks) or 0.07 (32-row chunks) to stay inside the fp32 range; the recurrent entry and
- * FRWKV_PREFILL_RECURRENT take any rho in [0, 1]. */
+ * prefill kernel divides by the running product of rho over one 32-row chunk, so in retention mode that product
+ * must stay above 1e-36 (rho >= 0.08 on every row is enough); a chunk that violates it sets bit 1 of the prefill
+ * entry's error_flag instead of passing inf/NaN on silently.  The recurrent entry and FRWKV_PREFILL_RECURRENT take
+ * any rho in [0, 1]. */
 enum { FRWKV_DECAY_LOGITS = 0, FRWKV_DECAY_RETENTION = 1 };
 /* metadata error bits written to status[0]; same values as
  * csrc/validation/recurrent_metadata.cu:15-22 */
@@ -86,7 +87,9 @@ int frwkv_sm100_wkv7_validate_metadata(
  * and neither it nor anything it calls allocates or frees memory.
  *   - pool_size above FRWKV_SM100_STATIC_POOL_SLOTS is rejected (FRWKV_ERR_UNSUPPORTED);
  *   - the first call on each device looks up the array's device address (a cheap runtime
- *     query made with that device current); make that first call outside any stream capture;
+ *     query made with that device current); make that first call outside any stream capture.
+ *     The per-device address cache is written without synchronisation: two host threads that make
+ *     their first call on one device at the same time both store the same value, which is harmless;
  *   - all calls on a device share the one array: the kernel re-initialises the part it uses
  *     at the start of every call, but two such calls that overlap in time on the GPU
  *     (different streams) would race, so keep them on one stream or otherwise ordered. */
@@ -112,7 +115,23 @@ int frwkv_sm100_wkv7_recurrent(
     const void* decay_bias, void* y, float* y_f32, int n_seq, int total_tokens, int heads,
     int io_dtype, int decay_mode, float scale, int max_seqlen, void* stream);
 
-/* Chunked prefill (chunk 64, WY/UT transform on tcgen05 tensor cores, fp32 state
+/* The fp16-state decode contract ("Albatross" family): fp16 tokens, fp16 state pool [slots, H, 64, 64] (half the
+ * state traffic of the fp32 contract), decay applied as S + S*delta with
+ * delta = fp16(rho - 1 + dither(phase)), phase = elapsed_pool[slot] + head*64 + key + token offset, the new state
+ * rounded to fp16 after every token and y = fp16(scale * r^T S) read from the rounded state; afterwards
+ * elapsed_pool[slot] advances by the sequence's token count (a second small launch).  Stands in for
+ * tmix_wkv7_recurrent_fp16_from_decay_logits and the kernels behind it
+ * (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:57-75,244-380,459-583,1204-1286; arithmetic as in
+ * its exact kernel :244-340 and the oracle tests/tmix/wkv7/test.py:88-149).  Same fail-closed rules: invalid
+ * metadata fills y with NaN and leaves state and elapsed counters untouched.
+ *   elapsed_pool : device int32 [slots];  state_pool_f16 : device fp16;  tokens, decay_bias, y : fp16. */
+int frwkv_sm100_wkv7_recurrent_fp16_state(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, int32_t* elapsed_pool,
+    void* state_pool_f16, const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* decay_bias, void* y, int n_seq, int total_tokens, int heads, int decay_mode, float scale,
+    int max_seqlen, void* stream);
+
+/* Chunked prefill (32-row chunks, WY/UT transform on tcgen05 tensor cores, fp32 state
  * carry), in place on the pool; stands in for the kernels behind
  * rl_infctx_tmix_wkv7_chunk_fp32io16_forward
  * (csrc/sm120/tmix/wkv7/rl_infctx_chunk_fp32io16_forward.cu:41-135,318-539 and
@@ -124,8 +143,13 @@ int frwkv_sm100_wkv7_recurrent(
  *                (4 bytes per sequence for batches of 2..2048 sequences), used to hand the
  *                sequences to the SMs longest first; NULL is accepted and keeps the natural
  *                order (same results, a longer tail on ragged batches);
- *   error_flag : optional device int32 that the tensor-core kernel sets nonzero if
- *                one of its bounded waits gave up (the output is then invalid). */
+ *   error_flag : optional device int32; the tensor-core kernel ORs in bit 0 if one of its bounded waits gave up
+ *                (that (sequence, head)'s rows of y are then NaN and its state slot keeps its old value) and bit 1
+ *                if a chunk's decay product left the fp32 range (retention mode only; the output is then invalid).
+ * The kernel's 16-bit operands are fp16 where they are bounded by the data: |state|, |r.k| sums and V beyond
+ * 65504 overflow to inf and show as NaN in y.  Tensor maps for the six token tensors are encoded on the host at
+ * the first call with a given (address, shape) and cached, so repeated calls on the same buffers make no driver
+ * call. */
 int frwkv_sm100_wkv7_prefill(
     const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
     const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,

@@ -57,10 +57,31 @@ def _case(seed, lengths, slots, pool_slots, heads, dtype, scales, bias_scale=Non
     return case
 
 
-def main(ref_root: str) -> None:
+def fp16_state(ref) -> None:
+    """The fp16-state decode contract: the reference's rwkv7_fp16_reference (tests/tmix/wkv7/test.py:88-149) on a
+    ragged fp16 case with bias, scale, permuted slots and nonzero elapsed counters."""
+    std = (0.12, 3.5, 0.06, 0.06, 0.06, 0.06)
+    case = _case(20260804 + 66, (1, 2, 4, 9, 33), [5, 0, 7, 2, 4], 9, 2, torch.float16, std, bias_scale=0.2)
+    state = case["state_pool"].half()
+    elapsed = torch.tensor([17, 0, 123456, 3, 99, 1 << 20, 7, 65535, 5], dtype=torch.int32)
+    y, final = ref.rwkv7_fp16_reference(
+        case["r"], case["decay_logits"], case["k"], case["v"], case["a"], case["b"], state_pool=state,
+        elapsed_state_pool=elapsed, cu_seqlens=case["cu_seqlens"], state_indices=case["state_indices"], scale=0.5,
+        decay_bias=case["decay_bias"])
+    blob = {k: _bits(v) for k, v in case.items() if v is not None and k != "state_pool"}
+    blob.update(state_pool=_bits(state), elapsed_state_pool=elapsed.numpy(), y=_bits(y), final_pool=_bits(final),
+                scale=np.float64(0.5), dtype=np.array("torch.float16"))
+    np.savez_compressed(OUT / "recurrent_fp16_state.npz", **blob)
+    print("recurrent_fp16_state", tuple(y.shape), float(y.float().abs().max()))
+
+
+def main(ref_root: str, only: str | None = None) -> None:
     root = Path(ref_root)
     sys.path[:0] = [str(root), str(root / "tests")]
     ref = _load(root / "tests/tmix/wkv7/test.py", "ref_wkv7_test")
+    if only == "fp16_state":
+        fp16_state(ref)
+        return
     ref_chunk = _load(root / "tests/tmix/wkv7/rl_infctx/test.py", "ref_rl_infctx_test")
     std = (0.12, 3.5, 0.06, 0.06, 0.06, 0.06)
     cases = {
@@ -102,9 +123,10 @@ def main(ref_root: str) -> None:
                 dtype=np.array("torch.float16"))
     np.savez_compressed(OUT / "rl_infctx_fp16.npz", **blob)
     print("rl_infctx_fp16", tuple(y.shape))
+    fp16_state(ref)
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/FlashRWKV2")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/FlashRWKV2 [fp16_state]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

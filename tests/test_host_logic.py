@@ -80,7 +80,7 @@ def test_native_module_exports_reference_symbols():
 
     for name in ("prepare_tmix_wkv7_recurrent_metadata", "prepare_tmix_wkv7_recurrent_graph_metadata",
                  "tmix_wkv7_recurrent_fp32_from_decay_logits", "rl_infctx_tmix_wkv7_chunk_fp32io16_forward",
-                 "_RecurrentMetadataTicket", "tmix_wkv7_prefill_fp32"):
+                 "_RecurrentMetadataTicket", "tmix_wkv7_prefill_fp32", "tmix_wkv7_recurrent_fp16_from_decay_logits"):
         assert hasattr(ext, name), name
     def arg_names(fn):  # pybind functions carry their signature in the first docstring line
         head = fn.__doc__.splitlines()[0]
@@ -93,6 +93,9 @@ def test_native_module_exports_reference_symbols():
     assert arg_names(ext.rl_infctx_tmix_wkv7_chunk_fp32io16_forward)[:13] == [
         "sequence_chunk_offsets", "chunk_token_starts", "chunk_token_ends", "state", "r", "decay_logits", "k", "v",
         "a", "b", "strategy", "scale", "decay_bias"]
+    assert arg_names(ext.tmix_wkv7_recurrent_fp16_from_decay_logits) == [
+        "query_start_loc", "state_indices", "elapsed_state_pool", "state", "r", "decay_logits", "k", "v", "a", "b",
+        "output", "scale", "decay_bias", "validated_metadata", "max_seqlen"]
     assert arg_names(ext.prepare_tmix_wkv7_recurrent_metadata) == [
         "query_start_loc", "state_indices", "total_tokens", "state_pool_size", "max_seqlen"]
     assert arg_names(ext.prepare_tmix_wkv7_recurrent_graph_metadata) == [
@@ -113,6 +116,24 @@ def test_public_signature_matches_reference_contract():
         assert name in params
     with pytest.raises(TypeError, match="log_decay"):
         op(None, None, None, None, None, None, state_pool=None, cu_seqlens=None, log_decay=None)
+
+
+def test_fp16_state_signature_matches_reference_contract():
+    """rwkv-rs/FlashRWKV2 tests/tmix/wkv7/test.py:883-893: raw decay logits only, no elapsed alias."""
+    from flashrwkv2_b200.tmix.wkv7 import infer_tmix_wkv7_recurrent_fp16_forward_varlen as op
+
+    params = inspect.signature(op).parameters
+    for name in ("decay_logits", "state_pool", "elapsed_state_pool", "max_seqlen", "validated_metadata"):
+        assert name in params
+    assert "log_decay" not in params and "elapsed_t" not in params
+    t = torch.zeros(2, 1, 64, dtype=torch.float16)
+    with pytest.raises(TypeError, match="FP16-state state_pool"):
+        op(t, t, t, t, t, t, state_pool=torch.zeros(1, 1, 64, 64), elapsed_state_pool=torch.zeros(1, dtype=torch.int32),
+           cu_seqlens=torch.tensor([0, 2], dtype=torch.int32), state_indices=torch.tensor([0], dtype=torch.int32))
+    with pytest.raises(TypeError, match="torch.int32"):
+        op(t, t, t, t, t, t, state_pool=torch.zeros(1, 1, 64, 64, dtype=torch.float16),
+           elapsed_state_pool=torch.zeros(1, dtype=torch.int64), cu_seqlens=torch.tensor([0, 2], dtype=torch.int32),
+           state_indices=torch.tensor([0], dtype=torch.int32))
 
 
 def test_wrapper_rejections_happen_before_any_launch():

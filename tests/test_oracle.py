@@ -97,3 +97,22 @@ def test_chunked_wy_form_equals_token_loop(T):
                                    state_indices=[0], scale=0.7, decay_mode="retention")
     assert max_err_over_rms(torch.from_numpy(y), y_ref[:, 0]) < 1e-9
     assert max_err_over_rms(torch.from_numpy(S), p_ref[0, 0]) < 1e-9
+
+
+def test_fp16_state_oracle_reproduces_the_reference_function_exactly():
+    """The fp16-state decode contract: the restatement against the committed output of the reference's own
+    rwkv7_fp16_reference (tests/golden/make_golden.py): fp16 rounding after every token makes this bit-exact."""
+    from oracle.wkv7_oracle import wkv7_fp16_state_oracle
+
+    case = load_golden("recurrent_fp16_state")
+    y, pool, elapsed = wkv7_fp16_state_oracle(
+        *(case[n] for n in TOKEN_NAMES), state_pool=case["state_pool"], elapsed_state_pool=case["elapsed_state_pool"],
+        cu_seqlens=case["cu_seqlens"], state_indices=case["state_indices"], scale=case["scale"],
+        decay_bias=case["decay_bias"])
+    assert y.dtype == torch.float16 and pool.dtype == torch.float16
+    assert torch.equal(y, case["y"]) and torch.equal(pool, case["final_pool"])
+    lengths = (case["cu_seqlens"][1:] - case["cu_seqlens"][:-1]).tolist()
+    expected = case["elapsed_state_pool"].clone()
+    for slot, n in zip(case["state_indices"].tolist(), lengths):
+        expected[slot] += n
+    assert torch.equal(elapsed, expected)
