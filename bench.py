@@ -356,7 +356,8 @@ def measure_fp16_state_decode(args, local_rank):
     tok = {n: t[n].half() for n in "rkvab"}
     sig = (-torch.log(t["w"].float()) / 0.6065306597126334).clamp(1e-4, 1 - 1e-4)
     tok["w"] = torch.log(sig / (1 - sig)).half()  # the decay logits whose retention is w
-    pools = [t["state_pool"].half() for _ in range(2)]  # 2 x 1 GiB in rotation
+    pool = t["state_pool"].half()  # 1 GiB: every launch streams it from HBM
+    err = torch.zeros(1, dtype=torch.int32, device=device)
     elapsed = torch.zeros(n_seq, dtype=torch.int32, device=device)
     y = torch.empty_like(tok["v"])
     stream = torch.cuda.current_stream().cuda_stream
@@ -364,9 +365,10 @@ def measure_fp16_state_decode(args, local_rank):
 
     def step(i):
         rc = lib.frwkv_sm100_wkv7_recurrent_fp16_state(
-            t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, elapsed.data_ptr(), pools[i % 2].data_ptr(),
+            t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, elapsed.data_ptr(), pool.data_ptr(), n_seq,
             tok["r"].data_ptr(), tok["w"].data_ptr(), tok["k"].data_ptr(), tok["v"].data_ptr(), tok["a"].data_ptr(),
-            tok["b"].data_ptr(), 0, y.data_ptr(), n_seq, tokens, heads, _lib.DECAY_LOGITS, 1.0, 1, stream)
+            tok["b"].data_ptr(), 0, y.data_ptr(), n_seq, tokens, heads, _lib.DECAY_LOGITS, 1.0, 1, err.data_ptr(),
+            stream)
         if rc:
             raise RuntimeError(_lib.last_error())
 
@@ -379,8 +381,8 @@ def measure_fp16_state_decode(args, local_rank):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo,
-                         "kernel": "wkv7_recurrent_stream_kernel<half state> + advance_elapsed_kernel"},
-            "clocks": sampler.stop()}
+                         "kernel": "wkv7_decode_fp16_state_kernel + advance_elapsed_kernel"},
+            "error_flag": int(err.item()), "clocks": sampler.stop()}
 
 
 def run_ours(args, rank, local_rank, world):

@@ -64,7 +64,7 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_recurrent.restype = ci
     lib.frwkv_sm100_wkv7_recurrent.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, vp]
     lib.frwkv_sm100_wkv7_recurrent_fp16_state.restype = ci
-    lib.frwkv_sm100_wkv7_recurrent_fp16_state.argtypes = [vp] * 13 + [ci, ci, ci, ci, cf, ci, vp]
+    lib.frwkv_sm100_wkv7_recurrent_fp16_state.argtypes = [vp] * 5 + [ci] + [vp] * 8 + [ci, ci, ci, ci, cf, ci, vp, vp]
     lib.frwkv_sm100_wkv7_prefill.restype = ci
     lib.frwkv_sm100_wkv7_prefill.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     lib.frwkv_sm100_wkv7_prefill_workspace_bytes.restype = sz

@@ -399,10 +399,11 @@ void tmix_wkv7_recurrent_fp16_from_decay_logits(torch::Tensor query_start_loc, t
   const c10::cuda::CUDAGuard guard(state.device());
   check_abi(frwkv_sm100_wkv7_recurrent_fp16_state(
       meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), elapsed_state.data_ptr<int>(),
-      state.data_ptr(), r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
-      decay_bias.has_value() ? decay_bias->data_ptr() : nullptr, output.data_ptr(), static_cast<int>(n),
-      static_cast<int>(r.size(0)), static_cast<int>(h), FRWKV_DECAY_LOGITS, static_cast<float>(scale),
-      static_cast<int>(meta.max_seqlen), at::cuda::getCurrentCUDAStream(state.device().index()).stream()));
+      state.data_ptr(), static_cast<int>(state.size(0)), r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(),
+      v.data_ptr(), a.data_ptr(), b.data_ptr(), decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
+      output.data_ptr(), static_cast<int>(n), static_cast<int>(r.size(0)), static_cast<int>(h), FRWKV_DECAY_LOGITS,
+      static_cast<float>(scale), static_cast<int>(meta.max_seqlen), nullptr,
+      at::cuda::getCurrentCUDAStream(state.device().index()).stream()));
 }
 
 void tmix_wkv7_prefill_fp32(torch::Tensor query_start_loc, torch::Tensor state_indices, torch::Tensor state,

@@ -468,15 +468,33 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
   }
 }
 
+int launch_decode_fp16_state(const int32_t* cu, const int32_t* slots, const int32_t* status, const int32_t* elapsed,
+                             void* pool, int pool_slots, const void* r, const void* w, const void* k, const void* v,
+                             const void* a, const void* b, const void* bias, void* y, int n_seq, int total_tokens,
+                             int heads, int decay_mode, float scale, int32_t* error_flag, cudaStream_t stream);
+
+// One-token steps (max_seqlen == 1) go to the TMA-fed ring kernel, everything else to the register-streaming
+// kernel; FRWKV_FP16_STATE_KERNEL=stream forces the latter (tuning hook, read once).
 int launch_recurrent_fp16_state(const int32_t* cu, const int32_t* slots, const int32_t* status, int32_t* elapsed,
-                                void* pool, const void* r, const void* w, const void* k, const void* v,
-                                const void* a, const void* b, const void* bias, void* y, int n_seq, int total_tokens,
-                                int heads, int decay_mode, float scale, int max_seqlen, cudaStream_t stream) {
-  RecurrentParams p{cu, slots, status, pool, elapsed, r, w, k, v, a, b, bias, y, nullptr, n_seq, total_tokens, heads,
-                    scale, 0};
-  const int parts = choose_parts(n_seq, heads, max_seqlen, 0);
-  const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
-  const int rc = dispatch_parts<__half, __half>(p, decay_mode == FRWKV_DECAY_LOGITS, parts, prefetch, stream);
+                                void* pool, int pool_slots, const void* r, const void* w, const void* k,
+                                const void* v, const void* a, const void* b, const void* bias, void* y, int n_seq,
+                                int total_tokens, int heads, int decay_mode, float scale, int max_seqlen,
+                                int32_t* error_flag, cudaStream_t stream) {
+  static const bool force_stream = [] {
+    const char* e = std::getenv("FRWKV_FP16_STATE_KERNEL");
+    return e != nullptr && e[0] == 's';
+  }();
+  int rc;
+  if (max_seqlen == 1 && !force_stream) {
+    rc = launch_decode_fp16_state(cu, slots, status, elapsed, pool, pool_slots, r, w, k, v, a, b, bias, y, n_seq,
+                                  total_tokens, heads, decay_mode, scale, error_flag, stream);
+  } else {
+    RecurrentParams p{cu, slots, status, pool, elapsed, r, w, k, v, a, b, bias, y, nullptr, n_seq, total_tokens,
+                      heads, scale, 0};
+    const int parts = choose_parts(n_seq, heads, max_seqlen, 0);
+    const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
+    rc = dispatch_parts<__half, __half>(p, decay_mode == FRWKV_DECAY_LOGITS, parts, prefetch, stream);
+  }
   if (rc != FRWKV_OK) return rc;
   advance_elapsed_kernel<<<(n_seq + 255) / 256, 256, 0, stream>>>(cu, slots, status, elapsed, n_seq);
   return check_launch("advance_elapsed_kernel");
@@ -486,18 +504,21 @@ int launch_recurrent_fp16_state(const int32_t* cu, const int32_t* slots, const i
 
 extern "C" int frwkv_sm100_wkv7_recurrent_fp16_state(
     const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, int32_t* elapsed_pool,
-    void* state_pool_f16, const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
-    const void* decay_bias, void* y, int n_seq, int total_tokens, int heads, int decay_mode, float scale,
-    int max_seqlen, void* stream) {
+    void* state_pool_f16, int pool_slots, const void* r, const void* w, const void* k, const void* v, const void* a,
+    const void* b, const void* decay_bias, void* y, int n_seq, int total_tokens, int heads, int decay_mode,
+    float scale, int max_seqlen, int32_t* error_flag, void* stream) {
   using namespace frwkv;
   if (elapsed_pool == nullptr) return fail(FRWKV_ERR_ARGUMENT, "wkv7_recurrent_fp16_state: elapsed_pool must be non-null");
+  if (pool_slots <= 0) return fail(FRWKV_ERR_ARGUMENT, "wkv7_recurrent_fp16_state: pool_slots must be positive");
+  if ((reinterpret_cast<uintptr_t>(state_pool_f16) & 1023) != 0 && max_seqlen == 1)
+    max_seqlen = 0;  // the TMA-fed kernel wants the pool 1024-byte aligned; any other pool takes the streaming kernel
   int rc = check_wkv7_arguments("wkv7_recurrent_fp16_state", cu_seqlens, slots, static_cast<float*>(state_pool_f16), r, w,
                                 k, v, a, b, decay_bias, y, nullptr, n_seq, total_tokens, heads, FRWKV_IO_FP16,
                                 decay_mode, scale);
   if (rc != FRWKV_OK) return rc;
-  return launch_recurrent_fp16_state(cu_seqlens, slots, status, elapsed_pool, state_pool_f16, r, w, k, v, a, b,
-                                     decay_bias, y, n_seq, total_tokens, heads, decay_mode, scale, max_seqlen,
-                                     static_cast<cudaStream_t>(stream));
+  return launch_recurrent_fp16_state(cu_seqlens, slots, status, elapsed_pool, state_pool_f16, pool_slots, r, w, k, v,
+                                     a, b, decay_bias, y, n_seq, total_tokens, heads, decay_mode, scale, max_seqlen,
+                                     error_flag, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int frwkv_sm100_wkv7_recurrent(

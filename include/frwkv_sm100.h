@@ -124,12 +124,15 @@ int frwkv_sm100_wkv7_recurrent(
  * (csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:57-75,244-380,459-583,1204-1286; arithmetic as in
  * its exact kernel :244-340 and the oracle tests/tmix/wkv7/test.py:88-149).  Same fail-closed rules: invalid
  * metadata fills y with NaN and leaves state and elapsed counters untouched.
- *   elapsed_pool : device int32 [slots];  state_pool_f16 : device fp16;  tokens, decay_bias, y : fp16. */
+ *   elapsed_pool : device int32 [pool_slots];  state_pool_f16 : device fp16 [pool_slots, H, 64, 64];
+ *   tokens, decay_bias, y : fp16;  max_seqlen : 1 for a decode step (every row one token: the TMA-fed kernel,
+ *   which wants the pool 1024-byte aligned), the largest row length otherwise (<= 0 if unknown);
+ *   error_flag : optional device int32, bit 0 set if a bounded wait of the decode kernel gave up. */
 int frwkv_sm100_wkv7_recurrent_fp16_state(
     const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, int32_t* elapsed_pool,
-    void* state_pool_f16, const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
-    const void* decay_bias, void* y, int n_seq, int total_tokens, int heads, int decay_mode, float scale,
-    int max_seqlen, void* stream);
+    void* state_pool_f16, int pool_slots, const void* r, const void* w, const void* k, const void* v, const void* a,
+    const void* b, const void* decay_bias, void* y, int n_seq, int total_tokens, int heads, int decay_mode,
+    float scale, int max_seqlen, int32_t* error_flag, void* stream);
 
 /* Chunked prefill (32-row chunks, WY/UT transform on tcgen05 tensor cores, fp32 state
  * carry), in place on the pool; stands in for the kernels behind

@@ -57,6 +57,28 @@ def _run(case, **kw):
     return y.cpu(), pool.cpu(), elapsed.cpu()
 
 
+def _run_c_abi(case, max_seqlen):
+    """Through the C ABI: max_seqlen = 1 selects the TMA-fed ring kernel, 0 the register-streaming kernel."""
+    from flashrwkv2_b200 import _lib
+
+    lib = _lib.load()
+    d = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    pool, elapsed = d["state_pool"].clone(), d["elapsed_state_pool"].clone()
+    y = torch.empty_like(d["v"])
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    total, heads, _ = d["v"].shape
+    rc = lib.frwkv_sm100_wkv7_recurrent_fp16_state(
+        d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, elapsed.data_ptr(), pool.data_ptr(),
+        pool.shape[0], *(d[n].data_ptr() for n in TOKEN_NAMES),
+        0 if d["decay_bias"] is None else d["decay_bias"].data_ptr(), y.data_ptr(), d["state_indices"].numel(), total,
+        heads, _lib.DECAY_LOGITS, float(case["scale"]), max_seqlen, err.data_ptr(),
+        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    return y.cpu(), pool.cpu(), elapsed.cpu()
+
+
 def _check(case, y, pool, elapsed, expected=None):
     if expected is None:
         expected = wkv7_fp16_state_oracle(
@@ -91,15 +113,55 @@ def test_golden_case_from_the_reference_function():
                                      (1, 15, 16, 17, 65)])
 def test_decode_and_short_rows(lengths):
     case = _case(lengths, heads=3, seed=len(lengths) + sum(lengths))
-    _check(case, *_run(case))
+    out = _run(case)
+    _check(case, *out)
+    if max(lengths) == 1:
+        # a decode step (every row one token) takes the TMA-fed ring kernel; the streaming kernel sums the key index
+        # in another order, so the two agree with the oracle to the same few units in the last place, not bit for bit
+        ring, stream = _run_c_abi(case, 1), _run_c_abi(case, 0)
+        _check(case, *ring)
+        _check(case, *stream)
+        assert all(torch.equal(x, z) for x, z in zip(ring, out))  # the operator picked the ring kernel by itself
 
 
-def test_many_heads_decode_step_and_rerun_is_bit_identical():
+@pytest.mark.parametrize("max_seqlen", (0, 1))
+def test_many_heads_decode_step_and_rerun_is_bit_identical(max_seqlen):
+    """64 sequences x 64 heads = 4096 items: every persistent CTA of the ring kernel (max_seqlen=1) goes round its
+    ring several times; permuted slots in a larger pool.  max_seqlen=0: the streaming kernel on the same batch."""
     case = _case((1,) * 64, heads=64, seed=5, pool_slots=70)
-    first = _run(case)
+    first = _run_c_abi(case, max_seqlen)
     _check(case, *first)
-    again = _run(case)
+    again = _run_c_abi(case, max_seqlen)
     assert all(torch.equal(x, z) for x, z in zip(first, again))
+
+
+def test_ring_kernel_skips_inactive_sequences_and_fails_closed():
+    """Capacity ticket with fewer active sequences than capacity, then duplicate slots: untouched state, NaN output."""
+    from flashrwkv2_b200.tmix.wkv7 import prepare_tmix_wkv7_recurrent_metadata
+
+    case = _case((1,) * 6, heads=2, seed=21, pool_slots=8, slots=[3, 1, 7, 0, 5, 2])
+    d = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    n_tok = torch.tensor([4], dtype=torch.int32, device=DEV)
+    n_seq = torch.tensor([4], dtype=torch.int32, device=DEV)
+    ticket = prepare_tmix_wkv7_recurrent_metadata(
+        d["cu_seqlens"], d["state_indices"], state_pool_size=8, token_capacity=6, sequence_capacity=6,
+        max_seqlen_capacity=1, num_active_tokens=n_tok, num_active_sequences=n_seq)
+    pool, elapsed = d["state_pool"].clone(), d["elapsed_state_pool"].clone()
+    y = _op()(*(d[n] for n in TOKEN_NAMES), state_pool=pool, elapsed_state_pool=elapsed, cu_seqlens=d["cu_seqlens"],
+              state_indices=d["state_indices"], scale=case["scale"], decay_bias=d["decay_bias"],
+              validated_metadata=ticket)
+    torch.cuda.synchronize()
+    active = dict(case, cu_seqlens=case["cu_seqlens"][:5], state_indices=case["state_indices"][:4])
+    for n in TOKEN_NAMES:
+        active[n] = case[n][:4]
+    y_ref, pool_ref, elapsed_ref = wkv7_fp16_state_oracle(
+        *(active[n] for n in TOKEN_NAMES), state_pool=case["state_pool"], elapsed_state_pool=case["elapsed_state_pool"],
+        cu_seqlens=active["cu_seqlens"], state_indices=active["state_indices"], scale=case["scale"],
+        decay_bias=case["decay_bias"])
+    assert relative_rmse(y[:4].cpu(), y_ref) <= TIGHT and relative_rmse(pool.cpu(), pool_ref) <= TIGHT
+    assert torch.equal(elapsed.cpu(), elapsed_ref)
+    for slot in (5, 2, 4, 6):  # inactive sequences' slots and unused slots
+        assert torch.equal(pool[slot].cpu(), case["state_pool"][slot])
 
 
 def test_steps_compose():
