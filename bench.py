@@ -385,6 +385,63 @@ def measure_fp16_state_decode(args, local_rank):
             "error_flag": int(err.item()), "clocks": sampler.stop()}
 
 
+def measure_fused_gate(args, local_rank):
+    """The fused kk / a-gate input form (five token tensors instead of six; a, b and the gated key formed in
+    registers): decode step at the c4_decode shapes and dense prefill at the c2 shapes, one GPU, device-resident."""
+    import torch
+
+    from flashrwkv2_b200 import _lib, dist as fdist
+    from flashrwkv2_b200.workloads import make_workload
+
+    device = torch.device("cuda", local_rank)
+    lib = _lib.load()
+    peaks, peak_kind = load_peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    out = {}
+    for name in ("c4_decode", "c2"):
+        wl = make_workload(name, device=device)
+        t = wl.tensors
+        n_seq, heads, tokens = wl.n_seq, wl.heads, wl.total_tokens
+        g = torch.Generator(device=device).manual_seed(17)
+        a12 = (torch.randn(t["k"].shape, generator=g, device=device) * 1.5).to(t["k"].dtype)
+        k_k = (1.0 + 0.3 * torch.randn(heads * 64, generator=g, device=device)).to(t["k"].dtype)
+        a0 = (0.5 * torch.randn(heads * 64, generator=g, device=device)).to(t["k"].dtype)
+        k_a = torch.rand(heads * 64, generator=g, device=device).to(t["k"].dtype)
+        y = torch.empty_like(t["v"])
+        err = torch.zeros(1, dtype=torch.int32, device=device)
+        need = lib.frwkv_sm100_wkv7_prefill_workspace_bytes(n_seq, tokens, heads)
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+        decode = name == "c4_decode"
+        head = (t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, t["state_pool"].data_ptr(),
+                t["r"].data_ptr(), t["w"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), a12.data_ptr(),
+                k_k.data_ptr(), a0.data_ptr(), k_a.data_ptr(), 0, y.data_ptr(), 0, n_seq, tokens, heads, _lib.IO_BF16,
+                _lib.DECAY_RETENTION, 1.0, max(wl.lengths))
+
+        def step(i):
+            if decode:
+                rc = lib.frwkv_sm100_wkv7_recurrent_fused_gate(*head, stream)
+            else:
+                rc = lib.frwkv_sm100_wkv7_prefill_fused_gate(*head, _lib.PREFILL_AUTO, ws.data_ptr(), need, err.data_ptr(),
+                                                             stream)
+            if rc:
+                raise RuntimeError(_lib.last_error())
+
+        ms_per_step, repeats = _timed_region(step, args.steps, args.warmup, fdist)
+        pairs, token_heads = n_seq * heads, tokens * heads
+        algo = pairs * (32768 + 5 * 128 + 128) if decode else token_heads * (5 * 128 + 128) + pairs * 32768
+        achieved = algo / (ms_per_step * 1e-3) / 1e9
+        out[name] = {"value": round(tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
+                     "ms_per_step": round(ms_per_step, 6), "repeats": repeats,
+                     "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                                  "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                                  "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo},
+                     "error_flag": int(err.item())}
+        del wl, t
+        torch.cuda.empty_cache()
+    out["workload"] = "five token tensors (r, w, raw k, v, a12) + per-channel k_k, a0, k_a; 640 B in + 128 B out per (token, head)"
+    return out
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
 
@@ -424,6 +481,11 @@ def run_ours(args, rank, local_rank, world):
             extras["c4_decode_fp16_state"] = measure_fp16_state_decode(args, local_rank)
         except RuntimeError as error:
             extras["c4_decode_fp16_state"] = {"error": str(error)}
+        torch.cuda.empty_cache()
+        try:
+            extras["fused_gate"] = measure_fused_gate(args, local_rank)
+        except RuntimeError as error:
+            extras["fused_gate"] = {"error": str(error)}
         torch.cuda.empty_cache()
         try:
             extras["gpu_baseline"] = gpu_baseline(torch.device("cuda", local_rank))
@@ -533,6 +595,27 @@ def gpu_baseline(device):
                                                            1.0, None)
         return step
 
+    if hasattr(ref, "tmix_wkv7_recurrent_fp16_from_decay_logits"):
+        # the reference's fp16-state decode family on the c1 shapes (fp16 tokens, decay logits)
+        wl16 = make_workload("c1", device=device)
+        t16 = wl16.tensors
+        tok = [t16[n].half() for n in names]
+        pool16 = t16["state_pool"].half()
+        elapsed = torch.zeros(pool16.shape[0], dtype=torch.int32, device=device)
+        y16 = torch.empty_like(tok[3])
+        tk = ref.prepare_tmix_wkv7_recurrent_metadata(t16["cu_seqlens"], t16["state_indices"], wl16.total_tokens,
+                                                      pool16.shape[0], 1)
+
+        def f16_step(i):
+            ref.tmix_wkv7_recurrent_fp16_from_decay_logits(t16["cu_seqlens"], t16["state_indices"], elapsed, pool16,
+                                                           *tok, y16, 1.0, None, tk, 1)
+
+        for i in range(5):
+            f16_step(i)
+        ms = _event_time_ms(f16_step, 200) / 200
+        out["decode_fp16_state"] = {"workload": "c1 shapes, fp16 state", "tokens_per_s": round(wl16.total_tokens / (ms * 1e-3), 1),
+                                    "us_per_step": round(ms * 1e3, 2)}
+        del wl16, t16, tok, pool16
     out["prefill"] = {"workload": "c2"}
     for label, fn in (("recurrent (wkv_fp32_v2_kernel)", recurrent_step),
                       ("rl_infctx chunk 64, recompute", chunk_step(1)),

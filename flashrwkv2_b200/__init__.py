@@ -47,6 +47,7 @@ def _load_native_backend():
 _C = _load_native_backend()
 
 from .tmix.wkv7 import (  # noqa: E402
+    infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen,
     infer_tmix_wkv7_prefill_fp32io16_forward_varlen,
     infer_tmix_wkv7_recurrent_fp16_forward_varlen,
     infer_tmix_wkv7_recurrent_fp32io16_forward_varlen,
@@ -55,6 +56,7 @@ from .tmix.wkv7 import (  # noqa: E402
 )
 
 __all__ = [
+    "infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen",
     "infer_tmix_wkv7_prefill_fp32io16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",

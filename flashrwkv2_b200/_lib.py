@@ -26,6 +26,8 @@ SYMBOLS = (
     "frwkv_sm100_wkv7_recurrent_fp16_state",
     "frwkv_sm100_wkv7_prefill",
     "frwkv_sm100_wkv7_prefill_workspace_bytes",
+    "frwkv_sm100_wkv7_recurrent_fused_gate",
+    "frwkv_sm100_wkv7_prefill_fused_gate",
 )
 
 _lib = None
@@ -69,6 +71,10 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_prefill.argtypes = [vp] * 13 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     lib.frwkv_sm100_wkv7_prefill_workspace_bytes.restype = sz
     lib.frwkv_sm100_wkv7_prefill_workspace_bytes.argtypes = [ci, ci, ci]
+    lib.frwkv_sm100_wkv7_recurrent_fused_gate.restype = ci
+    lib.frwkv_sm100_wkv7_recurrent_fused_gate.argtypes = [vp] * 15 + [ci, ci, ci, ci, ci, cf, ci, vp]
+    lib.frwkv_sm100_wkv7_prefill_fused_gate.restype = ci
+    lib.frwkv_sm100_wkv7_prefill_fused_gate.argtypes = [vp] * 15 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     return lib
 
 

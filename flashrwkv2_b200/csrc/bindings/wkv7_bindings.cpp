@@ -442,6 +442,69 @@ void tmix_wkv7_prefill_fp32(torch::Tensor query_start_loc, torch::Tensor state_i
       at::cuda::getCurrentCUDAStream(state.device().index()).stream()));
 }
 
+// The two in-place operators with the kk / a-gate producer fused in (see include/frwkv_sm100.h): `k` is the raw key
+// projection, `a12` the per-token gate logits, k_k / a0 / k_a the per-channel parameters [H*D] or [H,D].
+void check_gate_parameter(const torch::Tensor& parameter, const torch::Tensor& state, const torch::Tensor& r,
+                          const char* name) {
+  check_cuda_contiguous(parameter, name);
+  check_same_device(state, parameter, name);
+  TORCH_CHECK(parameter.scalar_type() == r.scalar_type(), name, " must match the token tensor dtype");
+  const int64_t h = state.size(1), d = state.size(2);
+  TORCH_CHECK((parameter.dim() == 1 && parameter.numel() == h * d) ||
+                  (parameter.dim() == 2 && parameter.size(0) == h && parameter.size(1) == d),
+              name, " must have shape [H*D] or [H,D]");
+}
+
+void tmix_wkv7_fused_gate_fp32(torch::Tensor query_start_loc, torch::Tensor state_indices, torch::Tensor state,
+                               torch::Tensor r, torch::Tensor decay_logits, torch::Tensor k, torch::Tensor v,
+                               torch::Tensor a12, torch::Tensor k_k, torch::Tensor a0, torch::Tensor k_a,
+                               torch::Tensor output, double scale, std::optional<torch::Tensor> decay_bias,
+                               TicketPtr validated_metadata, int64_t max_seqlen, const std::string& decay_mode,
+                               const std::string& strategy, std::optional<torch::Tensor> output_f32,
+                               std::optional<torch::Tensor> error_flag) {
+  const int mode = decay_code(decay_mode);
+  TORCH_CHECK(strategy == "decode" || strategy == "auto" || strategy == "recurrent" || strategy == "chunk_tc",
+              "strategy must be 'decode', 'auto', 'recurrent' or 'chunk_tc'");
+  const auto dims = check_recurrent_layout(query_start_loc, state_indices, state, r, decay_logits, k, v, a12, a12,
+                                           output, scale, false);
+  check_decay_bias(decay_bias, state, r, mode);
+  check_output_f32(output_f32, output);
+  check_gate_parameter(k_k, state, r, "k_k");
+  check_gate_parameter(a0, state, r, "a0");
+  check_gate_parameter(k_a, state, r, "k_a");
+  if (error_flag.has_value())
+    TORCH_CHECK(error_flag->is_cuda() && error_flag->scalar_type() == torch::kInt32 && error_flag->numel() >= 1,
+                "error_flag must be a CUDA int32 tensor");
+  const auto meta = resolve_metadata(query_start_loc, state_indices, state, r, validated_metadata, max_seqlen);
+  const c10::cuda::CUDAGuard guard(state.device());
+  const cudaStream_t stream = at::cuda::getCurrentCUDAStream(state.device().index()).stream();
+  const void* bias = decay_bias.has_value() ? decay_bias->data_ptr() : nullptr;
+  float* y32 = output_f32.has_value() ? output_f32->data_ptr<float>() : nullptr;
+  if (strategy == "decode") {
+    check_abi(frwkv_sm100_wkv7_recurrent_fused_gate(
+        meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), state.data_ptr<float>(),
+        r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a12.data_ptr(), k_k.data_ptr(), a0.data_ptr(),
+        k_a.data_ptr(), bias, output.data_ptr(), y32, static_cast<int>(dims.sequences), static_cast<int>(r.size(0)),
+        static_cast<int>(dims.heads), io_code(r), mode, static_cast<float>(scale), static_cast<int>(meta.max_seqlen),
+        stream));
+    return;
+  }
+  const int strategy_code = strategy == "auto" ? FRWKV_PREFILL_AUTO
+                            : strategy == "recurrent" ? FRWKV_PREFILL_RECURRENT : FRWKV_PREFILL_CHUNK_TC;
+  const size_t need = frwkv_sm100_wkv7_prefill_workspace_bytes(static_cast<int>(dims.sequences),
+                                                               static_cast<int>(r.size(0)),
+                                                               static_cast<int>(dims.heads));
+  torch::Tensor workspace;
+  if (need > 0) workspace = torch::empty({static_cast<int64_t>(need)}, state.options().dtype(torch::kUInt8));
+  check_abi(frwkv_sm100_wkv7_prefill_fused_gate(
+      meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), state.data_ptr<float>(),
+      r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a12.data_ptr(), k_k.data_ptr(), a0.data_ptr(),
+      k_a.data_ptr(), bias, output.data_ptr(), y32, static_cast<int>(dims.sequences), static_cast<int>(r.size(0)),
+      static_cast<int>(dims.heads), io_code(r), mode, static_cast<float>(scale), static_cast<int>(meta.max_seqlen),
+      strategy_code, need > 0 ? workspace.data_ptr() : nullptr, need,
+      error_flag.has_value() ? error_flag->data_ptr<int>() : nullptr, stream));
+}
+
 // Reference-shaped chunk forward: `state` is the gathered working state [B,H,D,D]; returns
 // (output, final_state) and leaves `state` untouched.  The reference's per-chunk host metadata is
 // accepted for signature compatibility; only the sequence boundaries it encodes are used (recovered
@@ -516,6 +579,13 @@ void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_& module) {
              py::arg("r"), py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"),
              py::arg("output"), py::arg("scale"), py::arg("decay_bias") = py::none(),
              py::arg("validated_metadata") = py::none(), py::arg("max_seqlen") = -1);
+  module.def("tmix_wkv7_fused_gate_fp32", &tmix_wkv7_fused_gate_fp32,
+             "WKV7 with the kk / a-gate producer fused in (decode kernel or prefill strategies), fp32 state in place",
+             py::arg("query_start_loc"), py::arg("state_indices"), py::arg("state"), py::arg("r"),
+             py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a12"), py::arg("k_k"), py::arg("a0"),
+             py::arg("k_a"), py::arg("output"), py::arg("scale"), py::arg("decay_bias") = py::none(),
+             py::arg("validated_metadata") = py::none(), py::arg("max_seqlen") = -1, py::arg("decay_mode") = "logits",
+             py::arg("strategy") = "auto", py::arg("output_f32") = py::none(), py::arg("error_flag") = py::none());
   module.def("tmix_wkv7_prefill_fp32", &tmix_wkv7_prefill_fp32,
              "WKV7 chunked prefill taking cu_seqlens directly, fp32 state in place", py::arg("query_start_loc"),
              py::arg("state_indices"), py::arg("state"), py::arg("r"), py::arg("decay_logits"), py::arg("k"),

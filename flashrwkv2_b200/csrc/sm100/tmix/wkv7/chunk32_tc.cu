@@ -82,7 +82,7 @@ static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one S
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColP = 0, kColQ = 64, kColU = 128, kColS = 192;
 
-template <typename io_t, bool LOGITS>
+template <typename io_t, bool LOGITS, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 2)
 wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   extern __shared__ uint8_t smem_raw[];
@@ -133,7 +133,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tma_prefetch_descriptor(&maps.k);
     tma_prefetch_descriptor(&maps.v);
     tma_prefetch_descriptor(&maps.a);
-    tma_prefetch_descriptor(&maps.b);
+    if constexpr (!FUSED) tma_prefetch_descriptor(&maps.b);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -147,13 +147,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 
   auto issue_tma = [&](int chunk_index) {  // one thread
     const int row = t_begin + chunk_index * kChunk;
-    mbar_expect_tx(bar_tma, 6 * kRawTile);
+    mbar_expect_tx(bar_tma, (FUSED ? 5 : 6) * kRawTile);  // the fused producer form has no b tensor
     tma_load_3d(smem + kOffRaw + 0 * kRawTile, &maps.r, bar_tma, 0, head, row);
     tma_load_3d(smem + kOffRaw + 1 * kRawTile, &maps.w, bar_tma, 0, head, row);
     tma_load_3d(smem + kOffRaw + 2 * kRawTile, &maps.k, bar_tma, 0, head, row);
     tma_load_3d(smem + kOffRaw + 3 * kRawTile, &maps.v, bar_tma, 0, head, row);
     tma_load_3d(smem + kOffRaw + 4 * kRawTile, &maps.a, bar_tma, 0, head, row);
-    tma_load_3d(smem + kOffRaw + 5 * kRawTile, &maps.b, bar_tma, 0, head, row);
+    if constexpr (!FUSED) tma_load_3d(smem + kOffRaw + 5 * kRawTile, &maps.b, bar_tma, 0, head, row);
   };
   if (tid == 0) issue_tma(0);
   bool tma_in_flight = true;
@@ -222,6 +222,15 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   long long phase_t0 = clock64();
 #endif
   const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
+  // fused kk / a-gate producer (csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu:131-156
+  // of the reference): this thread's two key channels of the per-head parameters
+  float2 gate_kk = make_float2(0.f, 0.f), gate_a0 = gate_kk, gate_ka = gate_kk;
+  if constexpr (FUSED) {
+    const int at = head * kHeadDim + 2 * lane;
+    gate_kk = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_kk) + at));
+    gate_a0 = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_a0) + at));
+    gate_ka = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_ka) + at));
+  }
 
   // ---- operand preparation of one chunk (decay products, scaled operands) -----------------------------------
   // It depends on the tokens only, so it runs for chunk c+1 while the tensor pipe works on chunk c's last
@@ -337,9 +346,27 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       float2 r2 = unpack2<io_t>(raw_r[t * 32 + kp]);
       float2 k2 = unpack2<io_t>(raw_k[t * 32 + kp]);
       float2 a2 = unpack2<io_t>(raw_a[t * 32 + kp]);
-      float2 b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
+      float2 b2 = make_float2(0.f, 0.f);
+      if constexpr (!FUSED) b2 = unpack2<io_t>(raw_b[t * 32 + kp]);
       if (t >= rows) {  // rows past the end of the sequence belong to somebody else (or are the loader's zero fill)
         r2 = k2 = a2 = b2 = make_float2(0.f, 0.f);
+      }
+      if constexpr (FUSED) {
+        // k2 is the raw key and a2 the gate logit a12: kk = normalize(k * k_k) over the 64 channels of the row (the
+        // 32 lanes hold two each), a = -kk, b = kk * g, k' = k * (1 + (g - 1) * k_a), g = sigmoid(a0 + a12); the three
+        // results are rounded to the token dtype where the reference's producer kernel stores them
+        const float2 u = make_float2(k2.x * gate_kk.x, k2.y * gate_kk.y);
+        float ss = fmaf(u.x, u.x, u.y * u.y);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float inv = 1.0f / fmaxf(sqrtf(ss), 1.0e-12f);
+        const float2 g2 = make_float2(1.0f / (1.0f + __expf(-(gate_a0.x + a2.x))), 1.0f / (1.0f + __expf(-(gate_a0.y + a2.y))));
+        const float2 kk = make_float2(u.x * inv, u.y * inv);
+        auto rnd = [](float x) { return to_f32(from_f32<io_t>(x)); };
+        a2 = make_float2(rnd(-kk.x), rnd(-kk.y));
+        b2 = make_float2(rnd(kk.x * g2.x), rnd(kk.y * g2.y));
+        k2 = make_float2(rnd(k2.x * fmaf(g2.x, gate_ka.x, 1.0f - gate_ka.x)), rnd(k2.y * fmaf(g2.y, gate_ka.y, 1.0f - gate_ka.y)));
+        if (t >= rows) a2 = b2 = k2 = make_float2(0.f, 0.f);
       }
       const uint32_t row_a = 2 * (t >> 3) * kRowGroup + (t & 7) * 16;  // At row of token t: 16*(t/8) + t%8
       const uint32_t row_r = row_a + kRowGroup;                        // Rt row: eight further
@@ -786,13 +813,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 }
 
 // The shared-memory attribute is set once per device and kernel instance, not on every call.
-template <typename io_t, bool LOGITS>
+template <typename io_t, bool LOGITS, bool FUSED>
 int prepare_kernel() {
   static bool done[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return check_launch("cudaGetDevice");
   if (!done[device]) {
-    if (cudaFuncSetAttribute(wkv7_chunk32_tc_kernel<io_t, LOGITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(wkv7_chunk32_tc_kernel<io_t, LOGITS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes) != cudaSuccess)
       return check_launch("wkv7_chunk32_tc_kernel shared-memory attribute");
     done[device] = true;  // benign race: two threads may both set the same attribute
@@ -800,11 +827,11 @@ int prepare_kernel() {
   return FRWKV_OK;
 }
 
-template <typename io_t>
+template <typename io_t, bool FUSED>
 int launch_typed32(const ChunkParams& p, const Maps& maps, bool logits, cudaStream_t stream) {
-  const int rc = logits ? prepare_kernel<io_t, true>() : prepare_kernel<io_t, false>();
+  const int rc = logits ? prepare_kernel<io_t, true, FUSED>() : prepare_kernel<io_t, false, FUSED>();
   if (rc != FRWKV_OK) return rc;
-  auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true> : wkv7_chunk32_tc_kernel<io_t, false>;
+  auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true, FUSED> : wkv7_chunk32_tc_kernel<io_t, false, FUSED>;
   const long long ctas = static_cast<long long>(p.n_seq) * p.heads;
   if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: too many (sequence, head) pairs");
   kernel<<<static_cast<unsigned>(ctas), kThreads, kSmemBytes, stream>>>(p, maps);
@@ -825,18 +852,29 @@ int& test_skip_commit_chunk() {
 int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, const int32_t* order, int len_from, int32_t* error_flag, cudaStream_t stream) {
+                      float scale, const int32_t* order, int len_from, int32_t* error_flag, const void* const* gate,
+                      cudaStream_t stream) {
   const bool bf16 = io_dtype == FRWKV_IO_BF16;
   chunk::Maps maps;
-  const int map_rc = chunk::make_maps(&maps, r, w, k, v, a, b, total_tokens, heads, bf16, kChunk);
+  const int map_rc = chunk::make_maps(&maps, r, w, k, v, a, gate != nullptr ? a : b, total_tokens, heads, bf16, kChunk);
   if (map_rc != FRWKV_OK) return map_rc;
-  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order, len_from};
+  chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order,
+                       len_from, nullptr, nullptr, nullptr};
+  if (gate != nullptr) {
+    p.gate_kk = gate[0];
+    p.gate_a0 = gate[1];
+    p.gate_ka = gate[2];
+  }
 #ifdef FRWKV_TEST_HOOKS
   p.skip_commit_chunk = chunk::test_skip_commit_chunk();
 #endif
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
-  if (bf16) return launch_typed32<__nv_bfloat16>(p, maps, logits, stream);
-  return launch_typed32<__half>(p, maps, logits, stream);
+  if (gate != nullptr) {
+    if (bf16) return launch_typed32<__nv_bfloat16, true>(p, maps, logits, stream);
+    return launch_typed32<__half, true>(p, maps, logits, stream);
+  }
+  if (bf16) return launch_typed32<__nv_bfloat16, false>(p, maps, logits, stream);
+  return launch_typed32<__half, false>(p, maps, logits, stream);
 }
 
 }  // namespace frwkv

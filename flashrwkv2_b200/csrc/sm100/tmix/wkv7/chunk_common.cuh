@@ -55,6 +55,9 @@ struct ChunkParams {
   float scale;
   const int* order;  // CTA rank -> sequence, longest first (nullptr: natural order)
   int len_from;      // > 0: only sequences at least this long (shorter ones go to the recurrence kernel)
+  // fused kk / a-gate producer (all null, or all three [H*64] parameter vectors in the token dtype): with them k is
+  // the raw key projection, the `a` tensor holds the gate logits a12 and the `b` tensor is not read
+  const void *gate_kk, *gate_a0, *gate_ka;
 #ifdef FRWKV_TEST_HOOKS
   int skip_commit_chunk;  // chunk whose first MMA commit is left out, -1 = none
 #endif

@@ -13,11 +13,13 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
                             const void* r, const void* w, const void* k, const void* v, const void* a,
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
-                            int max_seqlen, int parts_override, int len_below, cudaStream_t stream);
+                            int max_seqlen, int parts_override, int len_below, const void* const* gate,
+                            cudaStream_t stream);
 int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* status, float* pool, const void* r,
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
-                      float scale, const int32_t* order, int len_from, int32_t* error_flag, cudaStream_t stream);
+                      float scale, const int32_t* order, int len_from, int32_t* error_flag, const void* const* gate,
+                      cudaStream_t stream);
 
 namespace {
 
@@ -59,7 +61,7 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
                     const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
                     float scale, int max_seqlen, int len_from, void* workspace, size_t workspace_bytes,
-                    int32_t* error_flag, cudaStream_t stream) {
+                    int32_t* error_flag, const void* const* gate, cudaStream_t stream) {
   (void)max_seqlen;
   const int32_t* order = nullptr;
   const size_t need = chunk_tc_workspace_bytes(n_seq, total_tokens, heads);
@@ -73,7 +75,7 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
     order = static_cast<const int32_t*>(workspace);
   }
   return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                           io_dtype, decay_mode, scale, order, len_from, error_flag, stream);
+                           io_dtype, decay_mode, scale, order, len_from, error_flag, gate, stream);
 }
 
 }  // namespace frwkv
@@ -82,19 +84,28 @@ extern "C" size_t frwkv_sm100_wkv7_prefill_workspace_bytes(int n_seq, int total_
   return frwkv::chunk_tc_workspace_bytes(n_seq, total_tokens, heads);
 }
 
-extern "C" int frwkv_sm100_wkv7_prefill(
-    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
-    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
-    const void* decay_bias, void* y, float* y_f32, int n_seq, int total_tokens, int heads,
-    int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy, void* workspace,
-    size_t workspace_bytes, int32_t* error_flag, void* stream) {
-  using namespace frwkv;
-  int rc = check_wkv7_arguments("wkv7_prefill", cu_seqlens, slots, state_pool, r, w, k, v, a, b, decay_bias, y,
-                                y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
+namespace frwkv {
+namespace {
+
+// Shared body of the two prefill entries.  `gate` = {k_k, a0, k_a} of the fused kk / a-gate producer (then k is the
+// raw key projection, a the gate logits a12 and b is not read), or nullptr.
+int prefill_impl(const char* who, const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status,
+                 float* state_pool, const void* r, const void* w, const void* k, const void* v, const void* a,
+                 const void* b, const void* decay_bias, void* y, float* y_f32, int n_seq, int total_tokens, int heads,
+                 int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy, void* workspace,
+                 size_t workspace_bytes, int32_t* error_flag, const void* const* gate, cudaStream_t s) {
+  int rc = check_wkv7_arguments(who, cu_seqlens, slots, state_pool, r, w, k, v, a, gate != nullptr ? a : b,
+                                decay_bias, y, y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
   if (rc != FRWKV_OK) return rc;
   if (strategy != FRWKV_PREFILL_AUTO && strategy != FRWKV_PREFILL_RECURRENT && strategy != FRWKV_PREFILL_CHUNK_TC)
-    return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: unknown strategy %d", strategy);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return fail(FRWKV_ERR_ARGUMENT, "%s: unknown strategy %d", who, strategy);
+  if (gate != nullptr) {
+    for (int i = 0; i < 3; ++i)
+      if (gate[i] == nullptr || (reinterpret_cast<uintptr_t>(gate[i]) & 15) != 0)
+        return fail(FRWKV_ERR_ARGUMENT, "%s: k_k, a0 and k_a must be non-null and 16-byte aligned", who);
+    if (io_dtype == FRWKV_IO_FP32)
+      return fail(FRWKV_ERR_UNSUPPORTED, "%s: the fused kk/a-gate input form takes float16 or bfloat16 tokens", who);
+  }
   if (strategy == FRWKV_PREFILL_AUTO) {
     // fp32 tokens ask for 1e-5 agreement: that is the CUDA-core recurrence.  Rows of a few tokens gain
     // nothing from 32-row chunks either.  A batch that may hold both kinds (continuous batching: decode
@@ -104,20 +115,47 @@ extern "C" int frwkv_sm100_wkv7_prefill(
     else {
       rc = launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
                                    n_seq, total_tokens, heads, io_dtype, decay_mode, scale, kShortRow - 1, 0,
-                                   kShortRow, s);
+                                   kShortRow, gate, s);
       if (rc != FRWKV_OK) return rc;
       return launch_chunk_tc(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32, n_seq,
                              total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, kShortRow, workspace,
-                             workspace_bytes, error_flag, s);
+                             workspace_bytes, error_flag, gate, s);
     }
   }
   if (strategy == FRWKV_PREFILL_CHUNK_TC) {
     if (io_dtype == FRWKV_IO_FP32)
-      return fail(FRWKV_ERR_UNSUPPORTED, "wkv7_prefill: the tensor-core chunk kernel takes float16 or bfloat16 tokens");
+      return fail(FRWKV_ERR_UNSUPPORTED, "%s: the tensor-core chunk kernel takes float16 or bfloat16 tokens", who);
     return launch_chunk_tc(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32, n_seq,
                            total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, workspace,
-                           workspace_bytes, error_flag, s);
+                           workspace_bytes, error_flag, gate, s);
   }
   return launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
-                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0, s);
+                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0, gate, s);
+}
+
+}  // namespace
+}  // namespace frwkv
+
+extern "C" int frwkv_sm100_wkv7_prefill(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* decay_bias, void* y, float* y_f32, int n_seq, int total_tokens, int heads,
+    int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy, void* workspace,
+    size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  return frwkv::prefill_impl("wkv7_prefill", cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y,
+                             y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, strategy,
+                             workspace, workspace_bytes, error_flag, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int frwkv_sm100_wkv7_prefill_fused_gate(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k_raw, const void* v, const void* a12, const void* gate_k_k,
+    const void* gate_a0, const void* gate_k_a, const void* decay_bias, void* y, float* y_f32, int n_seq,
+    int total_tokens, int heads, int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy,
+    void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  const void* gate[3] = {gate_k_k, gate_a0, gate_k_a};
+  return frwkv::prefill_impl("wkv7_prefill_fused_gate", cu_seqlens, slots, status, state_pool, r, w, k_raw, v, a12,
+                             nullptr, decay_bias, y, y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale,
+                             max_seqlen, strategy, workspace, workspace_bytes, error_flag, gate,
+                             static_cast<cudaStream_t>(stream));
 }

@@ -100,6 +100,7 @@ template <typename io_t> struct Pair {  // 2 consecutive token-dtype values
 template <typename io_t, int RPL> struct TokenRows {  // one token's operands for this lane
   RowVals<io_t, RPL> r, w, k, a, b;
   Pair<io_t> w2;  // the two key rows whose decay this lane evaluates for its row group (see the kernel)
+  Pair<io_t> g2;  // fused producer: gate logits a12 of the same two rows
   Quad<io_t> v;
 };
 
@@ -143,7 +144,17 @@ struct RecurrentParams {
   int n_seq, total_tokens, heads;
   float scale;
   int len_below;  // > 0: only sequences shorter than this (the rest belongs to another kernel of the same call)
+  // fused producer (all three non-null or all null): per-channel [H*64] parameters of the kk / a-gate.  With them
+  // k is the raw key projection and a is the per-token gate logit a12; b is not read.
+  const void *gate_kk, *gate_a0, *gate_ka;
 };
+
+// The gate of the reference's producer kernel (csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/
+// infer_fp16_forward_varlen.cu:52-106,131-156): sigmoid as 1 / (1 + exp(-x)) with the fast exponential.
+__device__ __forceinline__ float gate_sigmoid(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// The producer stores its three outputs in the token dtype; the fused path rounds at the same point so that it
+// reproduces the two-kernel pipeline.
+template <typename io_t> __device__ __forceinline__ float round_io(float x) { return to_f32(from_f32<io_t>(x)); }
 
 // Resident CTAs per SM asked of the compiler.  The one-token kernels are sized by bytes in flight: with an fp32
 // state 4 CTAs (128 registers) already saturate HBM; a warp of the fp16-state kernel carries half the bytes, so it
@@ -152,7 +163,7 @@ struct RecurrentParams {
 #ifndef FRWKV_HALF_STATE_MIN_CTAS
 #define FRWKV_HALF_STATE_MIN_CTAS 5
 #endif
-template <typename io_t, typename state_t, int PARTS, bool LOGITS, bool PREFETCH>
+template <typename io_t, typename state_t, int PARTS, bool LOGITS, bool PREFETCH, bool FUSED = false>
 __global__ void __launch_bounds__(kWarpsPerCta * 32,
                                   (PREFETCH || sizeof(io_t) == 4)
                                       ? 0 : (std::is_same<state_t, __half>::value ? FRWKV_HALF_STATE_MIN_CTAS : 4))
@@ -220,8 +231,29 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
   int phase0 = 0;  // fp16 state: dither phase of this lane's first decay row at the sequence's first token
   if constexpr (kHalfState) phase0 = p.elapsed[slot] + head * kHeadDim + my_rows - t_lo;
 
+  // fused producer: per-channel parameters of this lane's rows (kk scale, key gate mix) and of its two gate rows
+  RowVals<io_t, RPL> gate_kk, gate_ka;
+  Pair<io_t> gate_a0;
+  if constexpr (FUSED) {
+    gate_kk.load(static_cast<const io_t*>(p.gate_kk) + head * kHeadDim + row0);
+    gate_ka.load(static_cast<const io_t*>(p.gate_ka) + head * kHeadDim + row0);
+    gate_a0.load(static_cast<const io_t*>(p.gate_a0) + head * kHeadDim + my_rows);
+  }
+
   auto fetch = [&](TokenRows<io_t, RPL>& dst, int t) {
     const size_t row = (static_cast<size_t>(t) * p.heads + head) * kHeadDim;
+    if constexpr (FUSED) {  // a holds the gate logits a12: only this lane's two gate rows are needed; b is not read
+      dst.g2.load(ap + row + my_rows);
+      dst.k.load(kp + row + row0);
+      dst.r.load(rp + row + row0);
+      dst.v.load(vp + row + col);
+      if constexpr (kSharedDecay) {
+        dst.w2.load(wp + row + my_rows);
+      } else {
+        dst.w.load(wp + row + row0);
+      }
+      return;
+    }
     dst.a.load(ap + row + row0);
     if constexpr (kSharedDecay) {
       dst.w2.load(wp + row + my_rows);
@@ -243,10 +275,31 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
     } else {
       fetch(cur, t);
     }
+    // fused producer: kk = normalize(k * kk_scale) over the 64 channels (this lane's rows, then across the row
+    // groups), a = -kk, b = kk * g, k' = k * (1 + (g - 1) * k_a) with g = sigmoid(a0 + a12) shared like the decay
+    float inv_norm = 0.f, gate_mine[2] = {0.f, 0.f};
+    if constexpr (FUSED) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPL; ++i) {
+        const float u = cur.k.get(i) * gate_kk.get(i);
+        ss = fmaf(u, u, ss);
+      }
+#pragma unroll
+      for (int m = LPR; m < 32; m <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      inv_norm = 1.0f / fmaxf(sqrtf(ss), 1.0e-12f);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) gate_mine[e] = gate_sigmoid(to_f32(gate_a0.vals[e]) + to_f32(cur.g2.vals[e]));
+    }
     float4 sa = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < RPL; ++i) {
-      const float fa = cur.a.get(i);
+      float fa;
+      if constexpr (FUSED) {
+        fa = round_io<io_t>(-(cur.k.get(i) * gate_kk.get(i)) * inv_norm);
+      } else {
+        fa = cur.a.get(i);
+      }
       sa.x = fmaf(fa, S[i].x, sa.x);
       sa.y = fmaf(fa, S[i].y, sa.y);
       sa.z = fmaf(fa, S[i].z, sa.z);
@@ -289,7 +342,17 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
       } else {
         fw = cur.w.get(i);
       }
-      const float fb = cur.b.get(i), fk = cur.k.get(i), fr = cur.r.get(i);
+      float fb, fk;
+      const float fr = cur.r.get(i);
+      if constexpr (FUSED) {
+        const float g = __shfl_sync(0xffffffffu, gate_mine[i & 1], group * LPR + (i >> 1));
+        const float raw = cur.k.get(i), ka = gate_ka.get(i);
+        fb = round_io<io_t>((raw * gate_kk.get(i)) * inv_norm * g);
+        fk = round_io<io_t>(raw * fmaf(g, ka, 1.0f - ka));
+      } else {
+        fb = cur.b.get(i);
+        fk = cur.k.get(i);
+      }
       if constexpr (kHalfState) {
         // S + S*delta + b*sa + k*v in fp32, then rounded to the stored precision; y reads the rounded state
         const float delta = fw;
@@ -367,7 +430,7 @@ int& test_recurrent_parts() {  // test build only: column split forced by the ne
 }
 #endif
 
-template <typename io_t, typename state_t, int PARTS, bool PREFETCH>
+template <typename io_t, typename state_t, int PARTS, bool PREFETCH, bool FUSED = false>
 int launch(const RecurrentParams& p, bool logits, cudaStream_t stream) {
   const long long warps = static_cast<long long>(p.n_seq) * p.heads * PARTS;
   const long long ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -384,23 +447,23 @@ int launch(const RecurrentParams& p, bool logits, cudaStream_t stream) {
   attribute[0].val.programmaticStreamSerializationAllowed = (!PREFETCH && pdl_enabled()) ? 1 : 0;
   config.attrs = attribute;
   config.numAttrs = 1;
-  auto kernel = logits ? wkv7_recurrent_stream_kernel<io_t, state_t, PARTS, true, PREFETCH>
-                       : wkv7_recurrent_stream_kernel<io_t, state_t, PARTS, false, PREFETCH>;
+  auto kernel = logits ? wkv7_recurrent_stream_kernel<io_t, state_t, PARTS, true, PREFETCH, FUSED>
+                       : wkv7_recurrent_stream_kernel<io_t, state_t, PARTS, false, PREFETCH, FUSED>;
   const cudaError_t err = cudaLaunchKernelEx(&config, kernel, p);
   if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_recurrent_stream_kernel: %s", cudaGetErrorString(err));
   return check_launch("wkv7_recurrent_stream_kernel");
 }
 
-template <typename io_t, typename state_t = float>
+template <typename io_t, typename state_t = float, bool FUSED = false>
 int dispatch_parts(const RecurrentParams& p, bool logits, int parts, bool prefetch, cudaStream_t stream) {
   if (!prefetch) {
-    if (parts == 2) return launch<io_t, state_t, 2, false>(p, logits, stream);
-    if (parts == 4) return launch<io_t, state_t, 4, false>(p, logits, stream);
-    return launch<io_t, state_t, 8, false>(p, logits, stream);
+    if (parts == 2) return launch<io_t, state_t, 2, false, FUSED>(p, logits, stream);
+    if (parts == 4) return launch<io_t, state_t, 4, false, FUSED>(p, logits, stream);
+    return launch<io_t, state_t, 8, false, FUSED>(p, logits, stream);
   }
-  if (parts == 2) return launch<io_t, state_t, 2, true>(p, logits, stream);
-  if (parts == 4) return launch<io_t, state_t, 4, true>(p, logits, stream);
-  return launch<io_t, state_t, 8, true>(p, logits, stream);
+  if (parts == 2) return launch<io_t, state_t, 2, true, FUSED>(p, logits, stream);
+  if (parts == 4) return launch<io_t, state_t, 4, true, FUSED>(p, logits, stream);
+  return launch<io_t, state_t, 8, true, FUSED>(p, logits, stream);
 }
 
 // column split: see launch_recurrent_stream
@@ -451,9 +514,15 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
                             const void* r, const void* w, const void* k, const void* v, const void* a,
                             const void* b, const void* bias, void* y, float* y_f32, int n_seq,
                             int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
-                            int max_seqlen, int parts_override, int len_below, cudaStream_t stream) {
+                            int max_seqlen, int parts_override, int len_below, const void* const* gate,
+                            cudaStream_t stream) {
   RecurrentParams p{cu, slots, status, pool, nullptr, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                    scale, len_below};
+                    scale, len_below, nullptr, nullptr, nullptr};
+  if (gate != nullptr) {
+    p.gate_kk = gate[0];
+    p.gate_a0 = gate[1];
+    p.gate_ka = gate[2];
+  }
   // Launch shape.  Decode (one token per row): the state is loaded, used once and stored,
   // so all that matters is bytes in flight; two column parts per pair keep every access a
   // full 128-byte line.  Long rows are a latency-bound token loop: thinner warps (more of
@@ -461,6 +530,13 @@ int launch_recurrent_stream(const int32_t* cu, const int32_t* slots, const int32
   const int parts = choose_parts(n_seq, heads, max_seqlen, parts_override);
   const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
+  if (gate != nullptr) {
+    switch (io_dtype) {
+      case FRWKV_IO_BF16: return dispatch_parts<__nv_bfloat16, float, true>(p, logits, parts, prefetch, stream);
+      case FRWKV_IO_FP16: return dispatch_parts<__half, float, true>(p, logits, parts, prefetch, stream);
+      default: return fail(FRWKV_ERR_UNSUPPORTED, "the fused kk/a-gate input form takes float16 or bfloat16 tokens");
+    }
+  }
   switch (io_dtype) {
     case FRWKV_IO_BF16: return dispatch_parts<__nv_bfloat16>(p, logits, parts, prefetch, stream);
     case FRWKV_IO_FP16: return dispatch_parts<__half>(p, logits, parts, prefetch, stream);
@@ -490,7 +566,7 @@ int launch_recurrent_fp16_state(const int32_t* cu, const int32_t* slots, const i
                                   total_tokens, heads, decay_mode, scale, error_flag, stream);
   } else {
     RecurrentParams p{cu, slots, status, pool, elapsed, r, w, k, v, a, b, bias, y, nullptr, n_seq, total_tokens,
-                      heads, scale, 0};
+                      heads, scale, 0, nullptr, nullptr, nullptr};
     const int parts = choose_parts(n_seq, heads, max_seqlen, 0);
     const bool prefetch = max_seqlen <= 0 || max_seqlen > 1;
     rc = dispatch_parts<__half, __half>(p, decay_mode == FRWKV_DECAY_LOGITS, parts, prefetch, stream);
@@ -531,8 +607,28 @@ extern "C" int frwkv_sm100_wkv7_recurrent(
                                 y, y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
   if (rc != FRWKV_OK) return rc;
   return launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32,
-                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0,
+                                 n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0, nullptr,
                                  static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int frwkv_sm100_wkv7_recurrent_fused_gate(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k_raw, const void* v, const void* a12, const void* gate_k_k,
+    const void* gate_a0, const void* gate_k_a, const void* decay_bias, void* y, float* y_f32, int n_seq,
+    int total_tokens, int heads, int io_dtype, int decay_mode, float scale, int max_seqlen, void* stream) {
+  using namespace frwkv;
+  if (!gate_k_k || !gate_a0 || !gate_k_a)
+    return fail(FRWKV_ERR_ARGUMENT, "wkv7_recurrent_fused_gate: k_k, a0 and k_a must be non-null");
+  int rc = check_wkv7_arguments("wkv7_recurrent_fused_gate", cu_seqlens, slots, state_pool, r, w, k_raw, v, a12, a12,
+                                decay_bias, y, y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale);
+  if (rc != FRWKV_OK) return rc;
+  const void* gate[3] = {gate_k_k, gate_a0, gate_k_a};
+  for (const void* q : gate)
+    if ((reinterpret_cast<uintptr_t>(q) & 15) != 0)
+      return fail(FRWKV_ERR_ARGUMENT, "wkv7_recurrent_fused_gate: tensors must be 16-byte aligned");
+  return launch_recurrent_stream(cu_seqlens, slots, status, state_pool, r, w, k_raw, v, a12, nullptr, decay_bias, y,
+                                 y_f32, n_seq, total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, 0, 0,
+                                 gate, static_cast<cudaStream_t>(stream));
 }
 
 #ifdef FRWKV_TEST_HOOKS

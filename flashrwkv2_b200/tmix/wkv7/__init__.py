@@ -157,9 +157,44 @@ def infer_tmix_wkv7_recurrent_fp16_forward_varlen(
     return y
 
 
+def infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen(
+        r: torch.Tensor, decay_logits: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a12: torch.Tensor, *,
+        k_k: torch.Tensor, a0: torch.Tensor, k_a: torch.Tensor, state_pool: torch.Tensor, cu_seqlens: torch.Tensor,
+        state_indices: torch.Tensor, scale: float = 1.0, decay_bias: torch.Tensor | None = None,
+        max_seqlen: int | None = None, validated_metadata: object | None = None, decay_mode: str = "logits",
+        strategy: str = "auto", output_f32: torch.Tensor | None = None,
+        error_flag: torch.Tensor | None = None) -> torch.Tensor:
+    """The in-place WKV7 operators with the kk / a-gate producer fused into their load stage.
+
+    The reference runs a separate kernel between the projections and WKV7 that writes three packed tensors
+    (flashrwkv2 wkv_prepare, csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu:52-106):
+    ``kk = normalize(k * k_k)`` per head, ``g = sigmoid(a0 + a12)``, ``a = -kk``, ``b = kk * g`` and the gated key
+    ``k * (1 + (g - 1) * k_a)``.  Here ``k`` is the raw key projection and ``a12`` the per-token gate logits; the
+    kernels form the three tensors in registers (rounded to the token dtype where the reference stores them), so they
+    are never written to or read from HBM.  ``strategy="decode"`` uses the register-streaming recurrence (decode
+    steps and short rows); "auto", "recurrent" and "chunk_tc" are the prefill strategies."""
+    tokens = (r, decay_logits, k, v, a12, a12)
+    check.packed_tokens(tokens)
+    check.fp32_pool(state_pool)
+    check.metadata(cu_seqlens, state_indices)
+    for name, value in (("k_k", k_k), ("a0", a0), ("k_a", k_a)):
+        check.tensor(value, name)
+    ticket = validated_metadata
+    if ticket is None:
+        ticket = prepare_tmix_wkv7_recurrent_metadata(
+            cu_seqlens, state_indices, total_tokens=r.shape[0], state_pool_size=state_pool.shape[0],
+            max_seqlen=max_seqlen)
+    y = torch.empty_like(v)
+    _extension().tmix_wkv7_fused_gate_fp32(
+        cu_seqlens, state_indices, state_pool, r, decay_logits, k, v, a12, k_k, a0, k_a, y, float(scale), decay_bias,
+        ticket, -1 if max_seqlen is None else int(max_seqlen), decay_mode, strategy, output_f32, error_flag)
+    return y
+
+
 from .rl_infctx import rl_infctx_tmix_wkv7_chunk_fp32io16  # noqa: E402
 
 __all__ = [
+    "infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen",
     "infer_tmix_wkv7_prefill_fp32io16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",

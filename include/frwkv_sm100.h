@@ -162,6 +162,29 @@ int frwkv_sm100_wkv7_prefill(
 
 size_t frwkv_sm100_wkv7_prefill_workspace_bytes(int n_seq, int total_tokens, int heads);
 
+/* The two entries above with the kk / a-gate producer fused into their operand-preparation stage.  The reference
+ * materialises a = -kk, b = kk * sigmoid(a0 + a12) and the gated key k' = k * (1 + (sigmoid(a0 + a12) - 1) * k_a) as
+ * three [total_tokens, H, 64] tensors before WKV7 (tmix_kk_a_gate kernels,
+ * csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu:52-106,131-156; oracle
+ * tests/tmix/wkv_prepare/test.py:103-126), kk = normalize(k * k_k) over the 64 channels of a head.  Here the caller
+ * passes what that kernel reads and the kernels form a, b and k' in registers, rounded to the token dtype where the
+ * reference stores them: five token tensors are read per (token, head) instead of six (640 B instead of 768 B
+ * besides y), and the producer's own pass over k and a12 with its three stores disappears.
+ *   k_raw : raw key projection;  a12 : per-token gate logits;  both [total_tokens, H, 64];
+ *   gate_k_k, gate_a0, gate_k_a : per-channel parameters [H*64];  all in the token dtype (bf16 or fp16).
+ * Everything else as in frwkv_sm100_wkv7_recurrent / frwkv_sm100_wkv7_prefill. */
+int frwkv_sm100_wkv7_recurrent_fused_gate(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k_raw, const void* v, const void* a12, const void* gate_k_k,
+    const void* gate_a0, const void* gate_k_a, const void* decay_bias, void* y, float* y_f32, int n_seq,
+    int total_tokens, int heads, int io_dtype, int decay_mode, float scale, int max_seqlen, void* stream);
+int frwkv_sm100_wkv7_prefill_fused_gate(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k_raw, const void* v, const void* a12, const void* gate_k_k,
+    const void* gate_a0, const void* gate_k_a, const void* decay_bias, void* y, float* y_f32, int n_seq,
+    int total_tokens, int heads, int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy,
+    void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

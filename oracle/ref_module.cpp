@@ -9,9 +9,22 @@
 
 void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_&);
 void register_rl_infctx_tmix_wkv7_chunk_forward_bindings(py::module_&);
+void register_infer_tmix_wkv7_recurrent_fp16_bindings(py::module_&);
+// host launcher of the reference's kk/a-gate kernels
+// (csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu:209-260); its own binding lives in the
+// wkv_prepare operator, which is not built here
+void tmix_kk_a_gate_forward_varlen_cuda(int batch_size, int max_seqlen, int total_tokens, int channels, int heads,
+                                        int head_size, torch::Tensor k, torch::Tensor k_k, torch::Tensor a0,
+                                        torch::Tensor a12, torch::Tensor k_a, torch::Tensor new_k, torch::Tensor neg_kk,
+                                        torch::Tensor kka);
 
 PYBIND11_MODULE(_C_ref, module) {
   module.doc() = "reference FlashRWKV2 WKV7 kernels, built unmodified for comparison";
   register_infer_tmix_wkv7_recurrent_fp32io16_bindings(module);
   register_rl_infctx_tmix_wkv7_chunk_forward_bindings(module);
+  register_infer_tmix_wkv7_recurrent_fp16_bindings(module);
+  module.def("tmix_kk_a_gate_forward_varlen", &tmix_kk_a_gate_forward_varlen_cuda, py::arg("batch_size"),
+             py::arg("max_seqlen"), py::arg("total_tokens"), py::arg("channels"), py::arg("heads"), py::arg("head_size"),
+             py::arg("k"), py::arg("k_k"), py::arg("a0"), py::arg("a12"), py::arg("k_a"), py::arg("new_k"),
+             py::arg("neg_kk"), py::arg("kka"));
 }

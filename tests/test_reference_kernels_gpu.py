@@ -188,3 +188,36 @@ def test_full_size_configurations_match_the_reference_kernels(ref, ours, name):
         a, b = y[lo:lo + (1 << 16)].float(), y_ref[lo:lo + (1 << 16)].float()
         tol = gate * rms + 2.0 ** -7 * torch.maximum(a.abs(), b.abs())  # one bf16 rounding step on top of the gate
         assert bool(((a - b).abs() <= tol).all()), (name, lo)
+
+
+def test_fp16_state_family_against_the_reference_kernels(ref):
+    """The fp16-state decode contract: the reference's own kernels (csrc/sm120/tmix/wkv7/
+    infer_recurrent_fp16_forward_varlen.{cpp,cu}, half2 arithmetic) and this library's through the same pybind symbol on
+    the same tensors.  Gate: the reference's relative RMSE for the family (3e-3, tests/fixtures/tolerances-v1.json:27-29);
+    elapsed counters equal; untouched slots bit-identical."""
+    import flashrwkv2_b200
+    from test_wkv7_fp16_state_gpu import _case
+
+    from oracle.wkv7_oracle import relative_rmse
+
+    if not hasattr(ref, "tmix_wkv7_recurrent_fp16_from_decay_logits"):
+        pytest.skip("oracle/_ref/_C_ref.so was built without the fp16-state family")
+    for lengths, heads in (((1,) * 64, 64), ((1, 2, 4, 9, 33), 2), ((8, 8), 3)):
+        case = _case(lengths, heads=heads, seed=31 + len(lengths))
+        d = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+        outs = []
+        for module in (ref, flashrwkv2_b200._C):
+            pool, elapsed = d["state_pool"].clone(), d["elapsed_state_pool"].clone()
+            y = torch.empty_like(d["v"])
+            module.tmix_wkv7_recurrent_fp16_from_decay_logits(
+                d["cu_seqlens"], d["state_indices"], elapsed, pool, *(d[n] for n in TOKEN_NAMES), y, float(case["scale"]),
+                d["decay_bias"], None, -1)
+            torch.cuda.synchronize()
+            outs.append((y.cpu(), pool.cpu(), elapsed.cpu()))
+        (y_r, pool_r, el_r), (y_o, pool_o, el_o) = outs
+        touched = case["state_indices"].tolist()
+        assert relative_rmse(y_o, y_r) <= 3e-3 and relative_rmse(pool_o[touched], pool_r[touched]) <= 3e-3
+        assert torch.equal(el_o, el_r)
+        for slot in range(pool_o.shape[0]):
+            if slot not in touched:
+                assert torch.equal(pool_o[slot], case["state_pool"][slot])
