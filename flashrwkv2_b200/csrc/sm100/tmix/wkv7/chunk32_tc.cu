@@ -359,8 +359,12 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         float ss = fmaf(u.x, u.x, u.y * u.y);
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-        const float inv = 1.0f / fmaxf(sqrtf(ss), 1.0e-12f);
-        const float2 g2 = make_float2(1.0f / (1.0f + __expf(-(gate_a0.x + a2.x))), 1.0f / (1.0f + __expf(-(gate_a0.y + a2.y))));
+        // SFU forms (rsqrt, ex2, rcp; 2^-22 relative): the values are rounded to 16 bits right below
+        float inv;
+        asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(fmaxf(ss, 1.0e-24f)));
+        float2 g2;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g2.x) : "f"(1.0f + fast_exp2(-kLog2e * (gate_a0.x + a2.x))));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(g2.y) : "f"(1.0f + fast_exp2(-kLog2e * (gate_a0.y + a2.y))));
         const float2 kk = make_float2(u.x * inv, u.y * inv);
         auto rnd = [](float x) { return to_f32(from_f32<io_t>(x)); };
         a2 = make_float2(rnd(-kk.x), rnd(-kk.y));

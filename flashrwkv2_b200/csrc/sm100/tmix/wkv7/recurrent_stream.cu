@@ -100,7 +100,7 @@ template <typename io_t> struct Pair {  // 2 consecutive token-dtype values
 template <typename io_t, int RPL> struct TokenRows {  // one token's operands for this lane
   RowVals<io_t, RPL> r, w, k, a, b;
   Pair<io_t> w2;  // the two key rows whose decay this lane evaluates for its row group (see the kernel)
-  Pair<io_t> g2;  // fused producer: gate logits a12 of the same two rows
+  Pair<io_t> g2, k2;  // fused producer: gate logits a12 and raw key of the same two rows
   Quad<io_t> v;
 };
 
@@ -231,20 +231,20 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
   int phase0 = 0;  // fp16 state: dither phase of this lane's first decay row at the sequence's first token
   if constexpr (kHalfState) phase0 = p.elapsed[slot] + head * kHeadDim + my_rows - t_lo;
 
-  // fused producer: per-channel parameters of this lane's rows (kk scale, key gate mix) and of its two gate rows
-  RowVals<io_t, RPL> gate_kk, gate_ka;
-  Pair<io_t> gate_a0;
+  // fused producer: every lane evaluates the gate for the same two key rows whose decay it evaluates (the 32 lanes
+  // of the warp cover the 64 rows exactly once), so it needs the per-channel parameters of those two rows only
+  Pair<io_t> gate_kk, gate_ka, gate_a0;
   if constexpr (FUSED) {
-    gate_kk.load(static_cast<const io_t*>(p.gate_kk) + head * kHeadDim + row0);
-    gate_ka.load(static_cast<const io_t*>(p.gate_ka) + head * kHeadDim + row0);
+    gate_kk.load(static_cast<const io_t*>(p.gate_kk) + head * kHeadDim + my_rows);
+    gate_ka.load(static_cast<const io_t*>(p.gate_ka) + head * kHeadDim + my_rows);
     gate_a0.load(static_cast<const io_t*>(p.gate_a0) + head * kHeadDim + my_rows);
   }
 
   auto fetch = [&](TokenRows<io_t, RPL>& dst, int t) {
     const size_t row = (static_cast<size_t>(t) * p.heads + head) * kHeadDim;
-    if constexpr (FUSED) {  // a holds the gate logits a12: only this lane's two gate rows are needed; b is not read
+    if constexpr (FUSED) {  // raw key and gate logits a12 of this lane's two gate rows only; b is not read
       dst.g2.load(ap + row + my_rows);
-      dst.k.load(kp + row + row0);
+      dst.k2.load(kp + row + my_rows);
       dst.r.load(rp + row + row0);
       dst.v.load(vp + row + col);
       if constexpr (kSharedDecay) {
@@ -275,28 +275,36 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
     } else {
       fetch(cur, t);
     }
-    // fused producer: kk = normalize(k * kk_scale) over the 64 channels (this lane's rows, then across the row
-    // groups), a = -kk, b = kk * g, k' = k * (1 + (g - 1) * k_a) with g = sigmoid(a0 + a12) shared like the decay
-    float inv_norm = 0.f, gate_mine[2] = {0.f, 0.f};
+    // fused producer, for this lane's two rows: kk = normalize(k * kk_scale) over the 64 channels (a full-warp sum:
+    // the lanes hold two rows each), a = -kk, b = kk * g, k' = k * (1 + (g - 1) * k_a), g = sigmoid(a0 + a12);
+    // rounded to the token dtype and handed to the lanes of the row group with shuffles
+    float own_a[2] = {0.f, 0.f}, own_b[2] = {0.f, 0.f}, own_k[2] = {0.f, 0.f};
     if constexpr (FUSED) {
-      float ss = 0.f;
+      float u[2], ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < RPL; ++i) {
-        const float u = cur.k.get(i) * gate_kk.get(i);
-        ss = fmaf(u, u, ss);
+      for (int e = 0; e < 2; ++e) {
+        u[e] = to_f32(cur.k2.vals[e]) * to_f32(gate_kk.vals[e]);
+        ss = fmaf(u[e], u[e], ss);
       }
+      // each of the 64 rows belongs to exactly one lane of this warp: a sum over all 32 lanes is the whole norm
 #pragma unroll
-      for (int m = LPR; m < 32; m <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-      inv_norm = 1.0f / fmaxf(sqrtf(ss), 1.0e-12f);
+      for (int m = 1; m < 32; m <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+      const float inv_norm = 1.0f / fmaxf(sqrtf(ss), 1.0e-12f);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) gate_mine[e] = gate_sigmoid(to_f32(gate_a0.vals[e]) + to_f32(cur.g2.vals[e]));
+      for (int e = 0; e < 2; ++e) {
+        const float g = gate_sigmoid(to_f32(gate_a0.vals[e]) + to_f32(cur.g2.vals[e]));
+        const float kk = u[e] * inv_norm, ka = to_f32(gate_ka.vals[e]);
+        own_a[e] = round_io<io_t>(-kk);
+        own_b[e] = round_io<io_t>(kk * g);
+        own_k[e] = round_io<io_t>(to_f32(cur.k2.vals[e]) * fmaf(g, ka, 1.0f - ka));
+      }
     }
     float4 sa = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < RPL; ++i) {
       float fa;
       if constexpr (FUSED) {
-        fa = round_io<io_t>(-(cur.k.get(i) * gate_kk.get(i)) * inv_norm);
+        fa = __shfl_sync(0xffffffffu, own_a[i & 1], group * LPR + (i >> 1));
       } else {
         fa = cur.a.get(i);
       }
@@ -345,10 +353,8 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
       float fb, fk;
       const float fr = cur.r.get(i);
       if constexpr (FUSED) {
-        const float g = __shfl_sync(0xffffffffu, gate_mine[i & 1], group * LPR + (i >> 1));
-        const float raw = cur.k.get(i), ka = gate_ka.get(i);
-        fb = round_io<io_t>((raw * gate_kk.get(i)) * inv_norm * g);
-        fk = round_io<io_t>(raw * fmaf(g, ka, 1.0f - ka));
+        fb = __shfl_sync(0xffffffffu, own_b[i & 1], group * LPR + (i >> 1));
+        fk = __shfl_sync(0xffffffffu, own_k[i & 1], group * LPR + (i >> 1));
       } else {
         fb = cur.b.get(i);
         fk = cur.k.get(i);
