@@ -99,14 +99,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     return;
   }
   const int active = p.status != nullptr ? p.status[2] : p.n_seq;
-  const int rank = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
-  if (rank >= p.n_seq) return;
-  const int seq = p.order != nullptr ? p.order[rank] : rank;
-  if (seq >= active || seq < 0 || seq >= p.n_seq) return;
-  const int t_begin = p.cu[seq], len = p.cu[seq + 1] - t_begin;
-  if (len <= 0 || len < p.len_from) return;
-  const int n_chunks = (len + kChunk - 1) / kChunk;
-  const int slot = p.slots[seq];
+  // The stream (sequence, head) and the range of its rows this CTA works on.  Direct mode: one stream per CTA, all of
+  // its rows.  Queue mode (p.queue != nullptr): CTAs are persistent and take (stream, segment) tasks from a counter;
+  // a segment is a run of `segment chunks` 32-row chunks, the state travels from a segment to the next through the
+  // pool slot, and a per-stream flag says how many segments are complete (see QueueHeader in chunk_common.cuh).
+  int head = 0, t_begin = 0, len = 0, n_chunks = 0, slot = 0, segment = 0;
+  bool last_segment = true;
+  int* segments_done = nullptr;  // queue mode: this stream's flag
 
   float* group_prod = reinterpret_cast<float*>(smem + kOffMisc);  // [8][64] retention products of each 4-row group
   uint64_t* bar_tma = reinterpret_cast<uint64_t*>(group_prod + kWarps * 64);
@@ -155,9 +154,9 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     tma_load_3d(smem + kOffRaw + 4 * kRawTile, &maps.a, bar_tma, 0, head, row);
     if constexpr (!FUSED) tma_load_3d(smem + kOffRaw + 5 * kRawTile, &maps.b, bar_tma, 0, head, row);
   };
-  if (tid == 0) issue_tma(0);
-  bool tma_in_flight = true;
+  bool tma_in_flight = false;
   uint32_t tma_parity = 0;
+  uint32_t chunks_done = 0;  // chunks of earlier tasks: bar_p and bar_state complete one phase per chunk
 
   // Fragment view of an accumulator block (tmem_ld_frag16): this thread holds rows frow0 and frow0 + 8 of its
   // quadrant and, of the 32 columns at 32*half, the pairs 8n + 2*fq + {0,1}, n = 0..3.
@@ -180,7 +179,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
   };
 
-  float* state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
+  float* state_g = nullptr;
   const bool compute_warp = warp < kWarps;
 
   constexpr uint32_t idesc_p = instr_desc_f16(64, 64, kMajorK, kMajorK, true);        // bf16 x bf16
@@ -221,16 +220,10 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 #ifdef FRWKV_CHUNK_TIMING
   long long phase_t0 = clock64();
 #endif
-  const io_t* bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
+  const io_t* bias_g = nullptr;
   // fused kk / a-gate producer (csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu:131-156
-  // of the reference): this thread's two key channels of the per-head parameters
+  // of the reference): this thread's two key channels of the per-head parameters (set per task)
   float2 gate_kk = make_float2(0.f, 0.f), gate_a0 = gate_kk, gate_ka = gate_kk;
-  if constexpr (FUSED) {
-    const int at = head * kHeadDim + 2 * lane;
-    gate_kk = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_kk) + at));
-    gate_a0 = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_a0) + at));
-    gate_ka = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_ka) + at));
-  }
 
   // ---- operand preparation of one chunk (decay products, scaled operands) -----------------------------------
   // It depends on the tokens only, so it runs for chunk c+1 while the tensor pipe works on chunk c's last
@@ -413,6 +406,66 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   };
 
   uint32_t mma_phase = 0;  // completed phases of bar_mma, counted the same way by every compute thread
+  volatile int* task_word = reinterpret_cast<volatile int*>(tmem_slot + 3);
+
+  for (bool first_task = true;; first_task = false) {
+  // ---- next task ------------------------------------------------------------------------------------------
+  // every warp has left the previous task; if that one was aborted (the compute warps carry `failed`), everybody
+  // leaves the loop together
+  if (__syncthreads_or(failed ? 1 : 0) != 0) break;
+  if (tid == 0) {
+    int task = -1;
+    if (p.queue != nullptr) {
+      task = atomicAdd(&p.queue->next_task, 1);
+      if (task >= p.queue->total_tasks) task = -1;
+    } else if (first_task) {
+      task = static_cast<int>(blockIdx.x);
+    }
+    *task_word = task;
+  }
+  __syncthreads();
+  const int task = *task_word;
+  if (task < 0) break;
+  {
+    int rank;
+    if (p.queue != nullptr) {
+      // tasks are numbered segment by segment; the streams that have a segment g are the first level_end[g] -
+      // level_end[g-1] ranks of the longest-first order, all heads of a rank next to each other
+      int g = 0;
+      while (g + 1 < kQueueLevels && task >= p.queue->level_end[g]) ++g;
+      const int in_level = task - (g > 0 ? p.queue->level_end[g - 1] : 0);
+      rank = in_level / p.heads;
+      head = in_level % p.heads;
+      segment = g;
+    } else {
+      rank = task / p.heads;
+      head = task % p.heads;
+      segment = 0;
+    }
+    if (rank >= p.n_seq) continue;
+    const int seq = p.order != nullptr ? p.order[rank] : rank;
+    if (seq >= active || seq < 0 || seq >= p.n_seq) continue;
+    const int seq_begin = p.cu[seq], seq_len = p.cu[seq + 1] - seq_begin;
+    if (seq_len <= 0 || seq_len < p.len_from) continue;
+    const int seg_rows = p.queue != nullptr ? p.queue->segment_chunks * kChunk : seq_len;
+    t_begin = seq_begin + segment * seg_rows;
+    len = min(seq_len - segment * seg_rows, seg_rows);
+    if (len <= 0) continue;
+    last_segment = segment * seg_rows + len >= seq_len;
+    n_chunks = (len + kChunk - 1) / kChunk;
+    slot = p.slots[seq];
+    state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
+    segments_done = p.queue != nullptr ? p.queue_flags + static_cast<size_t>(seq) * p.heads + head : nullptr;
+    bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
+    if constexpr (FUSED) {
+      const int at = head * kHeadDim + 2 * lane;
+      gate_kk = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_kk) + at));
+      gate_a0 = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_a0) + at));
+      gate_ka = unpack2<io_t>(*reinterpret_cast<const uint32_t*>(static_cast<const io_t*>(p.gate_ka) + at));
+    }
+  }
+  if (tid == 0) issue_tma(0);
+  tma_in_flight = true;
 
   if (compute_warp) {
     // =====================================================================================================
@@ -427,6 +480,22 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     scale_operands(0);
     release_v();
     release_bl();
+    // ---- queue mode, later segment: the previous segment of this stream must have stored its state.  Its task
+    // was handed out before this one, so the CTA that took it is running or done: the wait ends, and is bounded
+    // anyway.  The flag is read with acquire semantics by one thread; the barrier passes the ordering on.
+    if (segment > 0) {
+      if (tid == 0) {
+        int seen = 0;
+        for (int poll = 0; poll < (1 << 22); ++poll) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(segments_done) : "memory");
+          if (seen >= segment) break;
+          __nanosleep(200);
+        }
+        if (seen < segment) bad = true;
+      }
+      named_sync(kBarCompute, kComputeThreads);
+      __threadfence();
+    }
     // ---- initial state: global -> S0 operand tile (fp16) and -> TMEM (fp32, already times g_L of chunk 0) ----
     {
       uint32_t regs[32];
@@ -436,7 +505,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         uint8_t* op = smem + kOffOp + (arow & 7) * 16 + (arow >> 3) * kRowGroup;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float4 f0 = __ldcs(src + 2 * j), f1 = __ldcs(src + 2 * j + 1);
+          const float4 f0 = __ldcg(src + 2 * j), f1 = __ldcg(src + 2 * j + 1);  // L2: another SM may have written it
           uint32_t hi[4], lo[4];
           split2_f16(f0.x, f0.y, hi[0], lo[0]);
           split2_f16(f0.z, f0.w, hi[1], lo[1]);
@@ -477,7 +546,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       FRWKV_PHASE(0)
 
       // ================= P = X1 X2^T (issued during the previous chunk; Q = X1 S0 runs under the read-back) ====
-      bad |= !mbar_wait(bar_p, c & 1);
+      bad |= !mbar_wait(bar_p, (chunks_done + c) & 1);
       tcgen05_fence_after_sync();
       FRWKV_PHASE(2)
       // ================= read P: masks, A_ab -> fp32 scratch, others -> operand tiles =================
@@ -686,7 +755,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
           }
         }
       }
-      bad |= !mbar_wait(bar_state, c & 1);
+      bad |= !mbar_wait(bar_state, (chunks_done + c) & 1);
       tcgen05_fence_after_sync();
       // ---- state rows (all quadrants): S is final.  Next chunk: S -> S0 operand (fp16), g_L(next) S -> TMEM ----
       {
@@ -727,6 +796,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
         break;
       }
       FRWKV_PHASE(9)
+    }
+    // queue mode: the state of this segment is in the pool slot (stored by all compute threads before the barrier
+    // that ended the last chunk): publish it
+    if (!failed && segments_done != nullptr && tid == 0) {
+      __threadfence();
+      const int done = segment + 1;
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(segments_done), "r"(done) : "memory");
     }
   } else {
     // =====================================================================================================
@@ -787,14 +863,17 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
       }
       __syncwarp();
     }
-    // every MMA of this CTA has retired before anybody frees its TMEM (matters after an abort only: otherwise the
-    // compute warps have waited for the last state update)
-    if (lane == 0) {
-      mma_commit(bar_drain);
-      mbar_wait(bar_drain, 0);
-    }
-    __syncwarp();
   }
+  chunks_done += static_cast<uint32_t>(n_chunks);
+  }  // task loop
+
+  // every MMA of this CTA has retired before anybody frees its TMEM (matters after an abort only: otherwise the
+  // compute warps have waited for the last state update of every task)
+  if (!compute_warp && lane == 0) {
+    mma_commit(bar_drain);
+    mbar_wait(bar_drain, 0);
+  }
+  __syncwarp();
 
   if (failed) {
     if (tid == 0 && p.error_flag != nullptr) atomicOr(p.error_flag, kErrorWait);
@@ -836,8 +915,14 @@ int launch_typed32(const ChunkParams& p, const Maps& maps, bool logits, cudaStre
   const int rc = logits ? prepare_kernel<io_t, true, FUSED>() : prepare_kernel<io_t, false, FUSED>();
   if (rc != FRWKV_OK) return rc;
   auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true, FUSED> : wkv7_chunk32_tc_kernel<io_t, false, FUSED>;
-  const long long ctas = static_cast<long long>(p.n_seq) * p.heads;
+  long long ctas = static_cast<long long>(p.n_seq) * p.heads;
   if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: too many (sequence, head) pairs");
+  if (p.queue != nullptr) {  // persistent CTAs, two per SM
+    int device = 0, sms = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    ctas = 2LL * sms;
+  }
   kernel<<<static_cast<unsigned>(ctas), kThreads, kSmemBytes, stream>>>(p, maps);
   return check_launch("wkv7_chunk32_tc_kernel");
 }
@@ -857,13 +942,17 @@ int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* st
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
                       float scale, const int32_t* order, int len_from, int32_t* error_flag, const void* const* gate,
-                      cudaStream_t stream) {
+                      void* queue, cudaStream_t stream) {
   const bool bf16 = io_dtype == FRWKV_IO_BF16;
   chunk::Maps maps;
   const int map_rc = chunk::make_maps(&maps, r, w, k, v, a, gate != nullptr ? a : b, total_tokens, heads, bf16, kChunk);
   if (map_rc != FRWKV_OK) return map_rc;
   chunk::ChunkParams p{cu, slots, status, pool, bias, y, y_f32, error_flag, n_seq, total_tokens, heads, scale, order,
-                       len_from, nullptr, nullptr, nullptr};
+                       len_from, nullptr, nullptr, nullptr, nullptr, nullptr};
+  if (queue != nullptr) {  // header, then one flag per stream
+    p.queue = static_cast<chunk::QueueHeader*>(queue);
+    p.queue_flags = reinterpret_cast<int*>(p.queue + 1);
+  }
   if (gate != nullptr) {
     p.gate_kk = gate[0];
     p.gate_a0 = gate[1];

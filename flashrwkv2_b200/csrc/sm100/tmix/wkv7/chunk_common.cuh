@@ -42,6 +42,19 @@ int& test_skip_commit_chunk();
 constexpr int kErrorWait = 1;   // a bounded wait gave up
 constexpr int kErrorDecay = 2;  // the decay product of one chunk left the fp32 range (retention mode only)
 
+// Work queue of the persistent form of the chunk kernel (batches with more streams than CTA slots).  A stream
+// (sequence, head) is cut into segments of `segment_chunks` chunks; tasks are numbered segment level by segment
+// level, and within a level by the longest-first rank of the sequence and then by head, so a task's predecessor
+// (the same stream, one segment earlier) always has a smaller number and has been handed out before it.
+// level_end[g] = number of tasks in levels 0..g.  Filled on the device by sequence_order_kernel.
+constexpr int kQueueLevels = 16;
+struct QueueHeader {
+  int next_task;       // handed out with atomicAdd
+  int total_tasks;
+  int segment_chunks;  // chunks per segment
+  int level_end[kQueueLevels];
+};
+
 struct ChunkParams {
   const int* cu;
   const int* slots;
@@ -58,6 +71,8 @@ struct ChunkParams {
   // fused kk / a-gate producer (all null, or all three [H*64] parameter vectors in the token dtype): with them k is
   // the raw key projection, the `a` tensor holds the gate logits a12 and the `b` tensor is not read
   const void *gate_kk, *gate_a0, *gate_ka;
+  QueueHeader* queue;  // nullptr: one stream per CTA
+  int* queue_flags;    // [n_seq * heads] segments completed per stream (zeroed before the launch)
 #ifdef FRWKV_TEST_HOOKS
   int skip_commit_chunk;  // chunk whose first MMA commit is left out, -1 = none
 #endif

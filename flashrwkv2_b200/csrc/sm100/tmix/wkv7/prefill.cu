@@ -1,6 +1,7 @@
 // Prefill entry of the C ABI: strategy selection between the tensor-core chunk kernel
 // and the register-streaming recurrence.
 #include "../../common.cuh"
+#include "chunk_common.cuh"
 
 
 namespace frwkv {
@@ -19,7 +20,7 @@ int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* st
                       const void* w, const void* k, const void* v, const void* a, const void* b, const void* bias,
                       void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
                       float scale, const int32_t* order, int len_from, int32_t* error_flag, const void* const* gate,
-                      cudaStream_t stream);
+                      void* queue, cudaStream_t stream);
 
 namespace {
 
@@ -35,12 +36,28 @@ constexpr int kOrderThreads = 1024;
 
 __global__ void __launch_bounds__(kOrderThreads) sequence_order_kernel(const int* __restrict__ cu,
                                                                        const int* __restrict__ status, int n_seq,
-                                                                       int* __restrict__ order) {
+                                                                       int* __restrict__ order, int heads, int len_from,
+                                                                       chunk::QueueHeader* queue, int cta_slots) {
   __shared__ int len[kMaxOrdered];
+  __shared__ int level_count[chunk::kQueueLevels];
+  __shared__ int longest, shortest, live, segment_chunks_shared;
   const bool valid = status == nullptr || status[0] == 0;
   const int active = status == nullptr ? n_seq : status[2];
-  for (int i = threadIdx.x; i < n_seq; i += kOrderThreads)
+  if (threadIdx.x < chunk::kQueueLevels) level_count[threadIdx.x] = 0;
+  if (threadIdx.x == 0) {
+    longest = 0;
+    shortest = 0x7fffffff;
+    live = 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_seq; i += kOrderThreads) {
     len[i] = (valid && i < active) ? max(cu[i + 1] - cu[i], 0) : 0;
+    if (queue != nullptr && len[i] >= max(len_from, 1)) {  // the sequences the chunk kernel works on
+      atomicMax(&longest, len[i]);
+      atomicMin(&shortest, len[i]);
+      atomicAdd(&live, 1);
+    }
+  }
   __syncthreads();
   for (int i = threadIdx.x; i < n_seq; i += kOrderThreads) {
     const int mine = len[i];
@@ -48,12 +65,66 @@ __global__ void __launch_bounds__(kOrderThreads) sequence_order_kernel(const int
     for (int j = 0; j < n_seq; ++j) rank += (len[j] > mine) || (len[j] == mine && j < i);
     order[rank] = i;
   }
+  if (queue == nullptr) return;
+  // Work queue.  How many segments S to cut the longest sequence into: with N streams of about equal length on
+  // `cta_slots` persistent CTAs the launch takes ceil(N S / slots) / S stream times, and every segment costs about
+  // one and a half chunk times of start-up (first load, first operand preparation, state through the pool slot).
+  // S = 1 is the plain longest-first order; ragged batches keep it, it balances them by itself.
+  if (threadIdx.x == 0) {
+    const int chunks_longest = max(1, (longest + 31) / 32);
+    int best = 1;
+    if (live > 0 && shortest >= longest - longest / 10) {
+      float best_cost = 1e30f;
+      const long long streams = static_cast<long long>(live) * heads;
+      for (int S = 1; S <= chunk::kQueueLevels && S * 8 <= chunks_longest; ++S) {
+        const float rounds = static_cast<float>((streams * S + cta_slots - 1) / cta_slots) / S;
+        const float cost = rounds * (1.0f + 1.5f * S / chunks_longest);
+        if (cost < best_cost * 0.995f) {
+          best_cost = cost;
+          best = S;
+        }
+      }
+    }
+    segment_chunks_shared = (chunks_longest + best - 1) / best;
+  }
+  __syncthreads();
+  const int segment_chunks = segment_chunks_shared;
+  for (int i = threadIdx.x; i < n_seq; i += kOrderThreads) {
+    const int chunks = (len[i] + 31) / 32;
+    const int segments = len[i] >= max(len_from, 1) ? (chunks + segment_chunks - 1) / segment_chunks : 0;
+    for (int g = 0; g < segments; ++g) atomicAdd(&level_count[g], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int end = 0;
+    for (int g = 0; g < chunk::kQueueLevels; ++g) {
+      end += level_count[g] * heads;
+      queue->level_end[g] = end;
+    }
+    queue->total_tasks = end;
+    queue->segment_chunks = segment_chunks;
+    queue->next_task = 0;
+  }
 }
 
 }  // namespace
 
-size_t chunk_tc_workspace_bytes(int n_seq, int, int) {
-  return n_seq > 1 && n_seq <= kMaxOrdered ? static_cast<size_t>(n_seq) * sizeof(int) : 0;
+// Layout of the scratch: order[n_seq] (padded to 16 bytes), then, for batches with more streams than the GPU has
+// CTA slots, the work-queue header and one flag per (sequence, head).
+size_t order_bytes(int n_seq) { return (static_cast<size_t>(n_seq) * sizeof(int) + 15) & ~size_t(15); }
+int cta_slots() {  // two resident CTAs of the chunk kernel per SM
+  int device = 0, sms = 148;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  return 2 * sms;
+}
+bool wants_queue(int n_seq, int heads) { return static_cast<long long>(n_seq) * heads > 2LL * 148; }
+
+size_t chunk_tc_workspace_bytes(int n_seq, int, int heads) {
+  if (n_seq > kMaxOrdered) return 0;
+  if (wants_queue(n_seq, heads))
+    return order_bytes(n_seq) + sizeof(chunk::QueueHeader) + static_cast<size_t>(n_seq) * heads * sizeof(int);
+  return n_seq > 1 ? static_cast<size_t>(n_seq) * sizeof(int) : 0;
 }
 
 // The tensor-core path: optional longest-first ranking, then the 32-row chunk kernel.
@@ -64,18 +135,26 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
                     int32_t* error_flag, const void* const* gate, cudaStream_t stream) {
   (void)max_seqlen;
   const int32_t* order = nullptr;
+  void* queue = nullptr;
   const size_t need = chunk_tc_workspace_bytes(n_seq, total_tokens, heads);
-  if (need > 0 && workspace != nullptr) {  // no scratch given: natural order
-    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 3) != 0)
-      return fail(FRWKV_ERR_WORKSPACE, "wkv7_prefill: workspace of %zu bytes (4-byte aligned) needed, got %zu", need,
+  if (need > 0 && workspace != nullptr) {  // no scratch given: natural order, one CTA per stream
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0)
+      return fail(FRWKV_ERR_WORKSPACE, "wkv7_prefill: workspace of %zu bytes (16-byte aligned) needed, got %zu", need,
                   workspace_bytes);
-    sequence_order_kernel<<<1, kOrderThreads, 0, stream>>>(cu, status, n_seq, static_cast<int*>(workspace));
+    if (wants_queue(n_seq, heads)) {
+      queue = static_cast<char*>(workspace) + order_bytes(n_seq);
+      const size_t queue_bytes = sizeof(chunk::QueueHeader) + static_cast<size_t>(n_seq) * heads * sizeof(int);
+      if (cudaMemsetAsync(queue, 0, queue_bytes, stream) != cudaSuccess) return check_launch("work-queue memset");
+    }
+    sequence_order_kernel<<<1, kOrderThreads, 0, stream>>>(cu, status, n_seq, static_cast<int*>(workspace), heads,
+                                                           len_from, static_cast<chunk::QueueHeader*>(queue),
+                                                           cta_slots());
     const int rc = check_launch("sequence_order_kernel");
     if (rc != FRWKV_OK) return rc;
     order = static_cast<const int32_t*>(workspace);
   }
   return launch_chunk32_tc(cu, slots, status, pool, r, w, k, v, a, b, bias, y, y_f32, n_seq, total_tokens, heads,
-                           io_dtype, decay_mode, scale, order, len_from, error_flag, gate, stream);
+                           io_dtype, decay_mode, scale, order, len_from, error_flag, gate, queue, stream);
 }
 
 }  // namespace frwkv

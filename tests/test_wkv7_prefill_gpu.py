@@ -427,3 +427,23 @@ def test_prefill_operator_under_cuda_graph_capture():
             if slot not in touched:
                 assert torch.equal(state[slot], initial[slot])
         assert int(err.item()) == 0
+
+
+@pytest.mark.parametrize("lengths", [(2048,) * 10, (2047,) * 10, (4200, 2049, 2048, 2047, 64, 6200, 1, 33, 2112, 100)])
+def test_work_queue_hands_the_state_from_segment_to_segment(lengths):
+    """More streams than the GPU has CTA slots (10 sequences x 30 heads = 300 > 296): the chunk kernel runs with
+    persistent CTAs that take (stream, segment) tasks.  Equal lengths are cut into several segments (300 streams on
+    296 slots would otherwise take two rounds) whose state passes through the pool slot; the ragged batch keeps whole
+    streams in longest-first order.  Against the C oracle, and bit-identical to the same call without scratch (one
+    CTA per stream, no queue)."""
+    from flashrwkv2_b200 import _lib
+
+    case = _random_case(lengths, 30, torch.bfloat16, seed=404, slots=[3, 9, 0, 7, 1, 8, 2, 6, 4, 5], pool_slots=11)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y, y32, pool = _run_op(case, op="prefill", strategy="chunk_tc", error_flag=err)
+    _check(case, y, y32, pool, err, gate=TIGHT)
+    lib = _lib.load()
+    assert lib.frwkv_sm100_wkv7_prefill_workspace_bytes(10, sum(lengths), 30) > 10 * 30 * 4  # queue scratch asked for
+    y_direct, y32_direct, pool_direct, err_direct = _run_tc_c_abi(lib, case)  # passes no workspace
+    assert int(err_direct.item()) == 0
+    assert torch.equal(y, y_direct) and torch.equal(pool, pool_direct)
