@@ -442,6 +442,61 @@ def measure_fused_gate(args, local_rank):
     return out
 
 
+def measure_readout(args, local_rank):
+    """The recurrence kernel with the readout's elementwise stage (head norm, r.k residual, output gate) as its
+    epilogue, decode step at the c4_decode shapes, one GPU, device-resident: the plain input form (six token
+    tensors + the output gate in, the gated result out; y is not stored) and the form with the kk / a-gate
+    producer fused in as well (five token tensors + the gate)."""
+    import torch
+
+    from flashrwkv2_b200 import _lib, dist as fdist
+    from flashrwkv2_b200.workloads import make_workload
+
+    device = torch.device("cuda", local_rank)
+    lib = _lib.load()
+    peaks, peak_kind = load_peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    wl = make_workload("c4_decode", device=device)
+    t = wl.tensors
+    n_seq, heads, tokens = wl.n_seq, wl.heads, wl.total_tokens
+    dtype = t["k"].dtype
+    g = torch.Generator(device=device).manual_seed(23)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=device)
+    gate = rnd(*t["k"].shape).to(dtype)
+    a12 = (rnd(*t["k"].shape) * 1.5).to(dtype)
+    r_k, ln_w, ln_b = (0.2 * rnd(heads * 64)).to(dtype), (1.0 + 0.2 * rnd(heads * 64)).to(dtype), (0.1 * rnd(heads * 64)).to(dtype)
+    k_k, a0, k_a = (1.0 + 0.3 * rnd(heads * 64)).to(dtype), (0.5 * rnd(heads * 64)).to(dtype), torch.rand(heads * 64, generator=g, device=device).to(dtype)
+    x = torch.empty_like(t["v"])
+    out = {}
+    for label, fused in (("plain_inputs", False), ("fused_gate_inputs", True)):
+        call = (t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, t["state_pool"].data_ptr(),
+                t["r"].data_ptr(), t["w"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(),
+                a12.data_ptr() if fused else t["a"].data_ptr(), 0 if fused else t["b"].data_ptr(),
+                k_k.data_ptr() if fused else 0, a0.data_ptr() if fused else 0, k_a.data_ptr() if fused else 0, 0,
+                gate.data_ptr(), r_k.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(), x.data_ptr(), 0, 0, n_seq, tokens,
+                heads, _lib.IO_BF16, _lib.DECAY_RETENTION, 1.0, 1, stream)
+
+        def step(i):
+            rc = lib.frwkv_sm100_wkv7_recurrent_readout(*call)
+            if rc:
+                raise RuntimeError(_lib.last_error())
+
+        ms_per_step, repeats = _timed_region(step, args.steps, args.warmup, fdist)
+        pairs = n_seq * heads
+        algo = pairs * (32768 + (6 if fused else 7) * 128 + 128)
+        achieved = algo / (ms_per_step * 1e-3) / 1e9
+        out[label] = {"value": round(tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
+                      "ms_per_step": round(ms_per_step, 6), "repeats": repeats,
+                      "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                                   "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo}}
+    out["workload"] = ("c4_decode shapes; the token tensors + the output gate in, the gated readout result out "
+                       "(y not stored); the two-operator pipeline moves 768 B more per (token, head)")
+    del wl, t
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
 
@@ -486,6 +541,10 @@ def run_ours(args, rank, local_rank, world):
             extras["fused_gate"] = measure_fused_gate(args, local_rank)
         except RuntimeError as error:
             extras["fused_gate"] = {"error": str(error)}
+        try:
+            extras["readout_epilogue"] = measure_readout(args, local_rank)
+        except Exception as error:  # noqa: BLE001
+            extras["readout_epilogue"] = {"error": str(error)}
         torch.cuda.empty_cache()
         try:
             extras["gpu_baseline"] = gpu_baseline(torch.device("cuda", local_rank))
@@ -616,6 +675,24 @@ def gpu_baseline(device):
         out["decode_fp16_state"] = {"workload": "c1 shapes, fp16 state", "tokens_per_s": round(wl16.total_tokens / (ms * 1e-3), 1),
                                     "us_per_step": round(ms * 1e3, 2)}
         del wl16, t16, tok, pool16
+    if hasattr(ref, "tmix_lnx_rkvres_xg_forward_varlen"):
+        # the reference's elementwise readout kernel (consumer of y) on the c4_decode shapes: 2048 tokens x 64 heads.
+        # Timing only: its fp16 tensors are filled with small random values, kernel time does not depend on them.
+        rows, channels = 2048, 64 * 64
+        packed = [torch.randn(rows, channels, device=device).half() for _ in range(5)]
+        vectors = [torch.randn(channels, device=device).half() for _ in range(3)]
+        result = torch.empty(rows, channels, dtype=torch.float16, device=device)
+
+        def readout_step(i):
+            ref.tmix_lnx_rkvres_xg_forward_varlen(rows, 1, rows, channels, 64, 64, *packed[:4], *vectors, packed[4],
+                                                  result)
+
+        for i in range(5):
+            readout_step(i)
+        ms = _event_time_ms(readout_step, 200) / 200
+        out["readout_elementwise"] = {"workload": "c4_decode shapes (2048 x 64 heads), fp16; inputs may sit in L2",
+                                      "us_per_step": round(ms * 1e3, 2)}
+        del packed, result
     out["prefill"] = {"workload": "c2"}
     for label, fn in (("recurrent (wkv_fp32_v2_kernel)", recurrent_step),
                       ("rl_infctx chunk 64, recompute", chunk_step(1)),

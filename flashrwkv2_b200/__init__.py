@@ -49,6 +49,7 @@ _C = _load_native_backend()
 from .tmix.wkv7 import (  # noqa: E402
     infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen,
     infer_tmix_wkv7_prefill_fp32io16_forward_varlen,
+    infer_tmix_wkv7_readout_fp32io16_forward_varlen,
     infer_tmix_wkv7_recurrent_fp16_forward_varlen,
     infer_tmix_wkv7_recurrent_fp32io16_forward_varlen,
     prepare_tmix_wkv7_recurrent_metadata,
@@ -58,6 +59,7 @@ from .tmix.wkv7 import (  # noqa: E402
 __all__ = [
     "infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen",
     "infer_tmix_wkv7_prefill_fp32io16_forward_varlen",
+    "infer_tmix_wkv7_readout_fp32io16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",
     "prepare_tmix_wkv7_recurrent_metadata",

@@ -28,6 +28,7 @@ SYMBOLS = (
     "frwkv_sm100_wkv7_prefill_workspace_bytes",
     "frwkv_sm100_wkv7_recurrent_fused_gate",
     "frwkv_sm100_wkv7_prefill_fused_gate",
+    "frwkv_sm100_wkv7_recurrent_readout",
 )
 
 _lib = None
@@ -75,6 +76,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_recurrent_fused_gate.argtypes = [vp] * 15 + [ci, ci, ci, ci, ci, cf, ci, vp]
     lib.frwkv_sm100_wkv7_prefill_fused_gate.restype = ci
     lib.frwkv_sm100_wkv7_prefill_fused_gate.argtypes = [vp] * 15 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
+    lib.frwkv_sm100_wkv7_recurrent_readout.restype = ci
+    lib.frwkv_sm100_wkv7_recurrent_readout.argtypes = [vp] * 21 + [ci, ci, ci, ci, ci, cf, ci, vp]
     return lib
 
 

@@ -505,6 +505,59 @@ void tmix_wkv7_fused_gate_fp32(torch::Tensor query_start_loc, torch::Tensor stat
       error_flag.has_value() ? error_flag->data_ptr<int>() : nullptr, stream));
 }
 
+// WKV7 with the readout's elementwise stage (head norm, r.k residual, output gate) as epilogue.  `output` receives
+// the gated result that feeds the output projection; `wkv_output` (y itself) is stored only when given.  With
+// k_k, a0 and k_a the kk / a-gate producer is fused in as well: k is then the raw key, a the gate logits a12, and b
+// is not read.
+void tmix_wkv7_readout_fp32(torch::Tensor query_start_loc, torch::Tensor state_indices, torch::Tensor state,
+                            torch::Tensor r, torch::Tensor decay_logits, torch::Tensor k, torch::Tensor v,
+                            torch::Tensor a, std::optional<torch::Tensor> b, torch::Tensor out_gate,
+                            torch::Tensor r_k, torch::Tensor ln_weight, torch::Tensor ln_bias, torch::Tensor output,
+                            double scale, std::optional<torch::Tensor> k_k, std::optional<torch::Tensor> a0,
+                            std::optional<torch::Tensor> k_a, std::optional<torch::Tensor> decay_bias,
+                            TicketPtr validated_metadata, int64_t max_seqlen, const std::string& decay_mode,
+                            std::optional<torch::Tensor> wkv_output, std::optional<torch::Tensor> output_f32) {
+  const int mode = decay_code(decay_mode);
+  const bool fused = k_k.has_value() || a0.has_value() || k_a.has_value();
+  TORCH_CHECK(!fused || (k_k.has_value() && a0.has_value() && k_a.has_value()),
+              "k_k, a0 and k_a must be given together");
+  TORCH_CHECK(fused || b.has_value(), "b is required unless the kk / a-gate parameters are given");
+  const torch::Tensor& b_checked = fused ? a : *b;
+  const auto dims = check_recurrent_layout(query_start_loc, state_indices, state, r, decay_logits, k, v, a, b_checked,
+                                           output, scale, false);
+  TORCH_CHECK(r.scalar_type() != torch::kFloat32, "the readout epilogue takes float16 or bfloat16 tokens");
+  check_decay_bias(decay_bias, state, r, mode);
+  check_output_f32(output_f32, output);
+  TORCH_CHECK(out_gate.is_cuda() && out_gate.is_contiguous() && out_gate.device() == r.device() &&
+                  out_gate.scalar_type() == r.scalar_type() && out_gate.sizes() == r.sizes(),
+              "out_gate must match r's packed shape, dtype and device");
+  if (wkv_output.has_value())
+    TORCH_CHECK(wkv_output->is_cuda() && wkv_output->is_contiguous() && wkv_output->device() == r.device() &&
+                    wkv_output->scalar_type() == r.scalar_type() && wkv_output->sizes() == r.sizes(),
+                "wkv_output must match r's packed shape, dtype and device");
+  check_gate_parameter(r_k, state, r, "r_k");
+  check_gate_parameter(ln_weight, state, r, "ln_weight");
+  check_gate_parameter(ln_bias, state, r, "ln_bias");
+  if (fused) {
+    check_gate_parameter(*k_k, state, r, "k_k");
+    check_gate_parameter(*a0, state, r, "a0");
+    check_gate_parameter(*k_a, state, r, "k_a");
+  }
+  const auto meta = resolve_metadata(query_start_loc, state_indices, state, r, validated_metadata, max_seqlen);
+  const c10::cuda::CUDAGuard guard(state.device());
+  const cudaStream_t stream = at::cuda::getCurrentCUDAStream(state.device().index()).stream();
+  check_abi(frwkv_sm100_wkv7_recurrent_readout(
+      meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), state.data_ptr<float>(),
+      r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+      fused ? nullptr : b->data_ptr(), fused ? k_k->data_ptr() : nullptr, fused ? a0->data_ptr() : nullptr,
+      fused ? k_a->data_ptr() : nullptr, decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
+      out_gate.data_ptr(), r_k.data_ptr(), ln_weight.data_ptr(), ln_bias.data_ptr(), output.data_ptr(),
+      wkv_output.has_value() ? wkv_output->data_ptr() : nullptr,
+      output_f32.has_value() ? output_f32->data_ptr<float>() : nullptr, static_cast<int>(dims.sequences),
+      static_cast<int>(r.size(0)), static_cast<int>(dims.heads), io_code(r), mode, static_cast<float>(scale),
+      static_cast<int>(meta.max_seqlen), stream));
+}
+
 // Reference-shaped chunk forward: `state` is the gathered working state [B,H,D,D]; returns
 // (output, final_state) and leaves `state` untouched.  The reference's per-chunk host metadata is
 // accepted for signature compatibility; only the sequence boundaries it encodes are used (recovered
@@ -586,6 +639,15 @@ void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_& module) {
              py::arg("k_a"), py::arg("output"), py::arg("scale"), py::arg("decay_bias") = py::none(),
              py::arg("validated_metadata") = py::none(), py::arg("max_seqlen") = -1, py::arg("decay_mode") = "logits",
              py::arg("strategy") = "auto", py::arg("output_f32") = py::none(), py::arg("error_flag") = py::none());
+  module.def("tmix_wkv7_readout_fp32", &tmix_wkv7_readout_fp32,
+             "WKV7 recurrence with the readout's head norm, r.k residual and output gate as epilogue",
+             py::arg("query_start_loc"), py::arg("state_indices"), py::arg("state"), py::arg("r"),
+             py::arg("decay_logits"), py::arg("k"), py::arg("v"), py::arg("a"), py::arg("b"), py::arg("out_gate"),
+             py::arg("r_k"), py::arg("ln_weight"), py::arg("ln_bias"), py::arg("output"), py::arg("scale"),
+             py::arg("k_k") = py::none(), py::arg("a0") = py::none(), py::arg("k_a") = py::none(),
+             py::arg("decay_bias") = py::none(), py::arg("validated_metadata") = py::none(),
+             py::arg("max_seqlen") = -1, py::arg("decay_mode") = "logits", py::arg("wkv_output") = py::none(),
+             py::arg("output_f32") = py::none());
   module.def("tmix_wkv7_prefill_fp32", &tmix_wkv7_prefill_fp32,
              "WKV7 chunked prefill taking cu_seqlens directly, fp32 state in place", py::arg("query_start_loc"),
              py::arg("state_indices"), py::arg("state"), py::arg("r"), py::arg("decay_logits"), py::arg("k"),

@@ -191,11 +191,55 @@ def infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen(
     return y
 
 
+def infer_tmix_wkv7_readout_fp32io16_forward_varlen(
+        r: torch.Tensor, decay_logits: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
+        b: torch.Tensor | None, *, gate: torch.Tensor, r_k: torch.Tensor, ln_weight: torch.Tensor,
+        ln_bias: torch.Tensor, state_pool: torch.Tensor, cu_seqlens: torch.Tensor, state_indices: torch.Tensor,
+        scale: float = 1.0, k_k: torch.Tensor | None = None, a0: torch.Tensor | None = None,
+        k_a: torch.Tensor | None = None, decay_bias: torch.Tensor | None = None, max_seqlen: int | None = None,
+        validated_metadata: object | None = None, decay_mode: str = "logits",
+        wkv_output: torch.Tensor | None = None, output_f32: torch.Tensor | None = None,
+        output_weight: torch.Tensor | None = None) -> torch.Tensor:
+    """The in-place WKV7 recurrence followed, in the same kernel, by the elementwise stage of the reference's readout
+    (flashrwkv2/tmix/readout/__init__.py:10-77: head normalisation with eps 64e-5, ``sum(r*k*r_k) * v`` residual,
+    output gate): the recurrence's y never makes the round trip through HBM and r, k, v are not read a second time.
+
+    Returns the gated tensor ``[T, H, 64]`` that feeds the output projection, or, when ``output_weight`` ``[C, C]`` is
+    given, the projected ``[T, C]`` result (a plain library GEMM, as in the reference).  ``wkv_output`` and
+    ``output_f32``, when given, also receive the recurrence's own y.  With ``k_k``, ``a0`` and ``k_a`` the kk / a-gate
+    producer is fused in as well (``k`` raw, ``a`` = gate logits a12, ``b`` ignored).  Serves decode steps and short
+    rows through the register-streaming kernel; long prefill rows run correctly but at that kernel's rate."""
+    fused = k_k is not None or a0 is not None or k_a is not None
+    if fused and (k_k is None or a0 is None or k_a is None):
+        raise ValueError("k_k, a0 and k_a must be given together")
+    if not fused and b is None:
+        raise ValueError("b is required unless the kk / a-gate parameters are given")
+    check.packed_tokens((r, decay_logits, k, v, a, a if fused else b))
+    check.fp32_pool(state_pool)
+    check.metadata(cu_seqlens, state_indices)
+    for name, value in (("gate", gate), ("r_k", r_k), ("ln_weight", ln_weight), ("ln_bias", ln_bias)):
+        check.tensor(value, name)
+    ticket = validated_metadata
+    if ticket is None:
+        ticket = prepare_tmix_wkv7_recurrent_metadata(
+            cu_seqlens, state_indices, total_tokens=r.shape[0], state_pool_size=state_pool.shape[0],
+            max_seqlen=max_seqlen)
+    out = torch.empty_like(v)
+    _extension().tmix_wkv7_readout_fp32(
+        cu_seqlens, state_indices, state_pool, r, decay_logits, k, v, a, None if fused else b, gate, r_k, ln_weight,
+        ln_bias, out, float(scale), k_k, a0, k_a, decay_bias, ticket, -1 if max_seqlen is None else int(max_seqlen),
+        decay_mode, wkv_output, output_f32)
+    if output_weight is not None:
+        return torch.nn.functional.linear(out.reshape(out.shape[0], -1), output_weight)
+    return out
+
+
 from .rl_infctx import rl_infctx_tmix_wkv7_chunk_fp32io16  # noqa: E402
 
 __all__ = [
     "infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen",
     "infer_tmix_wkv7_prefill_fp32io16_forward_varlen",
+    "infer_tmix_wkv7_readout_fp32io16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",
     "prepare_tmix_wkv7_recurrent_metadata",

@@ -185,6 +185,27 @@ int frwkv_sm100_wkv7_prefill_fused_gate(
     int total_tokens, int heads, int io_dtype, int decay_mode, float scale, int max_seqlen, int strategy,
     void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
 
+/* WKV7 recurrence with the readout's elementwise stage as epilogue (decode and short rows; the register-streaming
+ * kernel serves every row length).  Replaces the pair of reference operators `wkv7 recurrent` + the first kernel of
+ * `readout` (flashrwkv2/tmix/readout/__init__.py:10-77; csrc/sm120/tmix/readout/infer_fp16_forward_varlen.cu:135-196;
+ * oracle tests/tmix/readout/test.py:43-66): per (token, head)
+ *   out = (headnorm(y) * ln_weight + ln_bias + (sum_c r_c k_c r_k_c) * v) * out_gate,   eps = 64e-5,
+ * with y rounded to the token dtype before the normalisation (what the two-operator pipeline stores and reads back) and
+ * k the key the recurrence consumes.  The output projection stays with the caller.
+ *   out_gate : [total_tokens, H, 64];  r_k, ln_weight, ln_bias : [H*64];  out : [total_tokens, H, 64]; token dtype
+ *              (bf16 or fp16);
+ *   y, y_f32 : optional stores of the recurrence's own output, or NULL;
+ *   gate_k_k, gate_a0, gate_k_a : all NULL, or all given: then k is the raw key, a the gate logits a12 and b is not
+ *              read (the input form of frwkv_sm100_wkv7_recurrent_fused_gate).
+ * Everything else as in frwkv_sm100_wkv7_recurrent.  Invalid metadata: `out` (and y when given) NaN-filled. */
+int frwkv_sm100_wkv7_recurrent_readout(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* gate_k_k, const void* gate_a0, const void* gate_k_a, const void* decay_bias,
+    const void* out_gate, const void* r_k, const void* ln_weight, const void* ln_bias, void* out,
+    void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
+    int max_seqlen, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,8 +7,8 @@ checkout, into oracle/_ref/_C_ref.so for sm_100:
 
 The sources are arch-neutral CUDA C++ (no inline PTX, no arch guards), so the only changes against the
 reference's own build are the target architecture and the module entry (oracle/ref_module.cpp, which
-registers the reference's recurrent (fp32- and fp16-state) and rl_infctx chunk bindings and wraps the host launcher
-of its kk/a-gate kernel).  Nothing is copied: nvcc and g++
+registers the reference's recurrent (fp32- and fp16-state) and rl_infctx chunk bindings and wraps the host launchers
+of its kk/a-gate and elementwise readout kernels).  Nothing is copied: nvcc and g++
 read the files in place, objects and the module go to oracle/_ref/ (git-ignored).  The module needs a GPU
 to do anything; tests and the bench use it as a second checker and as a same-GPU timing comparison.
 """
@@ -39,6 +39,7 @@ REFERENCE_SOURCES = (
     "csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cpp",  # the fp16-state decode family
     "csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu",
     "csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu",  # producer of a, b and the gated key
+    "csrc/sm120/tmix/readout/infer_fp16_forward_varlen.cu",  # consumer of y: head norm, r.k residual, gate
 )
 
 

@@ -116,3 +116,19 @@ def test_fp16_state_oracle_reproduces_the_reference_function_exactly():
     for slot, n in zip(case["state_indices"].tolist(), lengths):
         expected[slot] += n
     assert torch.equal(elapsed, expected)
+
+
+def test_readout_oracle_is_group_norm_plus_residual_times_gate():
+    """The readout restatement against an independent formulation: torch's group norm with one group per head
+    (eps 64e-5, as rwkv-rs/FlashRWKV2 csrc/sm120/tmix/readout/infer_fp16_forward_varlen.cu:25 sets it)."""
+    from oracle.wkv7_oracle import readout_prelinear_oracle
+
+    g = torch.Generator().manual_seed(12)
+    tokens, heads = 9, 5
+    y, r, k, v, gate = (torch.randn(tokens, heads, 64, generator=g) for _ in range(5))
+    r_k, ln_w, ln_b = (torch.randn(heads * 64, generator=g) for _ in range(3))
+    got = readout_prelinear_oracle(y, r, k, v, r_k, ln_w, ln_b, gate)
+    normed = torch.nn.functional.group_norm(y.reshape(tokens, heads * 64), heads, ln_w, ln_b, eps=64.0e-5)
+    residual = (r * k * r_k.reshape(1, heads, 64)).sum(-1, keepdim=True) * v
+    want = (normed.reshape(tokens, heads, 64) + residual) * gate
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)

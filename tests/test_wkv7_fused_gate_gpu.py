@@ -98,6 +98,30 @@ def test_recurrence_kernel_with_fused_gate(dtype, lengths):
     _check(case, *_fused(case, "decode"))
 
 
+def test_pipelined_decode_launch():
+    """Enough sequences (>= 8 per resident warp: 160 x 64 heads on 148 SMs) for the launch that walks several
+    sequences per warp with the next state staged through shared memory: the oracle at the bf16 gate (the largest
+    deviation over 40 M state elements is a neighbouring rounding of a large k' or b), and bit for bit the
+    one-sequence-per-warp launch (the same batch in calls of 40 sequences)."""
+    import flashrwkv2_b200.tmix.wkv7 as ops
+
+    case = _case((1,) * 160, 64, torch.float16, seed=8, bias=True)
+    y, y32, pool = _fused(case, "decode")
+    _check(case, y, y32, pool, gate=5e-3)
+    d = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    pool_small = d["state_pool"].clone()
+    pieces = []
+    cu = torch.arange(0, 41, dtype=torch.int32, device=DEV)
+    for lo in range(0, 160, 40):
+        pieces.append(ops.infer_tmix_wkv7_fused_gate_fp32io16_forward_varlen(
+            d["r"][lo:lo + 40], d["w"][lo:lo + 40], d["k"][lo:lo + 40], d["v"][lo:lo + 40], d["a12"][lo:lo + 40],
+            k_k=d["k_k"], a0=d["a0"], k_a=d["k_a"], state_pool=pool_small, cu_seqlens=cu,
+            state_indices=d["state_indices"][lo:lo + 40].contiguous(), scale=case["scale"],
+            decay_bias=d["decay_bias"], decay_mode=case["decay_mode"], strategy="decode"))
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat(pieces).cpu(), y) and torch.equal(pool_small.cpu(), pool)
+
+
 def test_decode_shape_retention_mode():
     case = _case((1,) * 64, 8, torch.bfloat16, seed=5, retention=True)
     _check(case, *_fused(case, "decode"))

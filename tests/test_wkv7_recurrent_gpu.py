@@ -184,6 +184,42 @@ def test_config1_decode_full_size():
     _assert_parity(case, *_run_op(case))
 
 
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("retention", (True, False))
+def test_pipelined_decode_launch(dtype, retention):
+    """One-token steps through the launch in which a warp walks several sequences and stages its next state through
+    shared memory (taken by default from 40 sequences per resident warp; the library's test build lowers that to 2,
+    so 150 x 20 heads suffice on 148 SMs).  Must equal the oracle and, bit for bit, the one-sequence-per-warp launch."""
+    from conftest import load_testhooks
+
+    from flashrwkv2_b200 import _lib
+
+    case = _random_case((1,) * 150, 20, dtype, seed=13, retention=retention)
+    d = _to_dev(case)
+    lib = load_testhooks()
+    io = _lib.IO_BF16 if dtype == torch.bfloat16 else _lib.IO_FP16
+    mode = _lib.DECAY_RETENTION if retention else _lib.DECAY_LOGITS
+    results = []
+    for rounds in (2, 1000):
+        pool = d["state_pool"].clone()
+        y = torch.empty_like(d["v"])
+        y32 = torch.empty(d["v"].shape, dtype=torch.float32, device=DEV)
+        lib.frwkv_sm100_test_pipeline_min_rounds(rounds)
+        try:
+            rc = lib.frwkv_sm100_wkv7_recurrent(
+                d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, pool.data_ptr(),
+                *(d[n].data_ptr() for n in TOKEN_NAMES), 0, y.data_ptr(), y32.data_ptr(), 150, 150, 20, io, mode,
+                case["scale"], 1, torch.cuda.current_stream().cuda_stream)
+        finally:
+            lib.frwkv_sm100_test_pipeline_min_rounds(0)
+        assert rc == 0
+        torch.cuda.synchronize()
+        results.append((y.cpu(), y32.cpu(), pool.cpu()))
+    _assert_parity(case, *results[0])
+    for got, want in zip(results[0], results[1]):
+        assert torch.equal(got, want)
+
+
 def test_run_to_run_bit_identical():
     case = _random_case((3, 1, 40, 7), 4, torch.bfloat16, seed=9)
     first = _run_op(case)
