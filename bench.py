@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload c4|c1|c2|c3|c4_decode|c4_prefill] [--no-extras] [--no-e2e]
+                    [--extra fp16_state|fused_gate|readout|gpu_baseline] [--min-region-s S]
 
 Default workload ``c4``: the 7B-width batch sharded by sequence over the N GPUs of one box (strong scaling: the
 total work is fixed, every rank keeps the sequences the longest-first sharder gives it, all sliced from the one
@@ -57,12 +58,14 @@ ALGO_FLOP_PREFILL_TOKEN_HEAD = 98304  # 12 GEMMs of 64^3 per 64 rows
 ALGO_BYTES_PREFILL_TOKEN_HEAD = 7 * 128
 ALGO_BYTES_PREFILL_PAIR = 32768
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per unit of work, from ncu captures of a small case
-# of the same kernel (traffic grows in proportion to the units): decode per (sequence, head), prefill per
-# (token, head).  Decode reads equal the algorithmic bytes; part of the written state is still dirty in L2 when
-# the kernel ends, so the write count is below the 16,512 bytes a pair writes.
-DECODE_TRAFFIC_PER_PAIR = (140538368 + 77164544) / 8192
-PREFILL_TRAFFIC_PER_TOKEN_HEAD = (810.2e6 + 125.6e6) / (32768 * 32)
+# DRAM bytes of one launch (read + written) per unit of work, from ncu captures (profiles/): decode per
+# (sequence, head), from captures of the c4_decode launch itself (131,072 pairs); prefill per (token, head), from a
+# capture of the c2 launch (traffic grows in proportion to the units).  Reads equal the algorithmic bytes; the
+# state written by the last CTAs is still dirty in L2 when a kernel ends, so the totals are 1-2 % below them.
+DECODE_TRAFFIC_PER_PAIR = 4.354e9 / 131072
+DECODE_FP16_STATE_TRAFFIC_PER_PAIR = 2.211e9 / 131072
+DECODE_READOUT_TRAFFIC_PER_PAIR = 4.383e9 / 131072
+PREFILL_TRAFFIC_PER_TOKEN_HEAD = (809.58e6 + 127.15e6) / (32768 * 32)
 MIN_REGION_S = 0.5
 
 DECODE_WORKLOADS = ("c1", "c4_decode")
@@ -379,7 +382,7 @@ def measure_fp16_state_decode(args, local_rank):
             "value": round(tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms_per_step, 6),
             "steps": args.steps, "repeats": repeats, "gpu_launches": 2 * args.steps * repeats,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": int(n_seq * heads * DECODE_FP16_STATE_TRAFFIC_PER_PAIR),
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo,
                          "kernel": "wkv7_decode_fp16_state_kernel + advance_elapsed_kernel"},
             "error_flag": int(err.item()), "clocks": sampler.stop()}
@@ -488,7 +491,7 @@ def measure_readout(args, local_rank):
         out[label] = {"value": round(tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
                       "ms_per_step": round(ms_per_step, 6), "repeats": repeats,
                       "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-                                   "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                                   "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None if fused else int(pairs * DECODE_READOUT_TRAFFIC_PER_PAIR),
                                    "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo}}
     out["workload"] = ("c4_decode shapes; the token tensors + the output gate in, the gated readout result out "
                        "(y not stored); the two-operator pipeline moves 768 B more per (token, head)")
@@ -751,7 +754,12 @@ def main():
     parser.add_argument("--workload", default="c4", choices=("c4", "c1", "c2", "c3", "c4_decode", "c4_prefill"))
     parser.add_argument("--no-extras", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--extra", default=None, choices=("fp16_state", "fused_gate", "readout", "gpu_baseline"),
+                        help="one GPU: measure only this block of the default run's extras and print it")
+    parser.add_argument("--min-region-s", type=float, default=MIN_REGION_S,
+                        help="shortest timed region (default 0.5 s); 0 for a profiler capture of a few launches")
     args = parser.parse_args()
+    globals()["MIN_REGION_S"] = max(0.0, args.min_region_s)
     if args.impl == "reference":
         # the reference arm is CPU code: hide the GPUs before torch (and the package) are imported, so that
         # none of the product's shared libraries is loaded into this process
@@ -778,6 +786,17 @@ def main():
     if world == 1 and args.gpus > 1:
         raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nnodes=1 "
                          f"--nproc-per-node {args.gpus} --master-addr 127.0.0.1 bench.py --gpus {args.gpus}")
+    if args.extra is not None:
+        if world != 1:
+            raise SystemExit("--extra runs on one GPU")
+        torch.cuda.set_device(local_rank)
+        block = {"fp16_state": lambda: measure_fp16_state_decode(args, local_rank),
+                 "fused_gate": lambda: measure_fused_gate(args, local_rank),
+                 "readout": lambda: measure_readout(args, local_rank),
+                 "gpu_baseline": lambda: gpu_baseline(torch.device("cuda", local_rank))}[args.extra]()
+        print(json.dumps({"extra": args.extra, **block}), flush=True)
+        fdist.shutdown()
+        return
     line = run_ours(args, rank, local_rank, world)
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -20,6 +20,7 @@
 // csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu:244-340, tests/tmix/wkv7/test.py:88-149 of
 // rwkv-rs/FlashRWKV2); the two kernels sum the key index in a different order, so they agree to a few fp16 units
 // in the last place, not bit for bit.
+#include <cstdlib>
 #include "../../common.cuh"
 #include "../../tcgen05.cuh"
 
@@ -367,8 +368,19 @@ int launch_decode_fp16_state(const int32_t* cu, const int32_t* slots, const int3
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const long long items = static_cast<long long>(n_seq) * heads;
   if (items > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_recurrent_fp16_state: too many (sequence, head) pairs");
-  const unsigned grid = static_cast<unsigned>(items < static_cast<long long>(sms) * kCtasPerSm
-                                                  ? items : static_cast<long long>(sms) * kCtasPerSm);
+  // Grid: the CTAs stride over the items, so any grid works.  Exactly the resident CTAs would fix every SM's share
+  // in advance, and SMs do not run equally fast; with up to 8 grids' worth of CTAs (at least 24 items each, so that
+  // filling the ring stays a small part of a CTA's life) the hardware scheduler evens that out: 406 -> 389 us on
+  // 2048 x 64 pairs.  FRWKV_FP16_GRID_MULT forces the multiple (tuning hook, read once).
+  static const int forced = [] {
+    const char* e = std::getenv("FRWKV_FP16_GRID_MULT");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  const long long resident = static_cast<long long>(sms) * kCtasPerSm;
+  long long mult = forced > 0 ? forced : items / (resident * 24);
+  mult = mult < 1 ? 1 : (mult > 8 && forced <= 0 ? 8 : mult);
+  const long long want = resident * mult;
+  const unsigned grid = static_cast<unsigned>(items < want ? items : want);
   DecodeParams p{cu, slots, status, elapsed, static_cast<__half*>(pool),
                  static_cast<const __half*>(r), static_cast<const __half*>(w), static_cast<const __half*>(k),
                  static_cast<const __half*>(v), static_cast<const __half*>(a), static_cast<const __half*>(b),
