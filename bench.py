@@ -495,6 +495,40 @@ def measure_readout(args, local_rank):
                                    "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo}}
     out["workload"] = ("c4_decode shapes; the token tensors + the output gate in, the gated readout result out "
                        "(y not stored); the two-operator pipeline moves 768 B more per (token, head)")
+    del wl, t, gate, a12, x
+    torch.cuda.empty_cache()
+    # prefill rows (c2 shapes): chunk kernel, then the readout stage as a second, HBM-bound launch over the stored y
+    wl = make_workload("c2", device=device)
+    t = wl.tensors
+    n_seq, heads, tokens = wl.n_seq, wl.heads, wl.total_tokens
+    gate = rnd(*t["k"].shape).to(dtype)
+    r_k, ln_w, ln_b = (0.2 * rnd(heads * 64)).to(dtype), (1.0 + 0.2 * rnd(heads * 64)).to(dtype), (0.1 * rnd(heads * 64)).to(dtype)
+    x, y = torch.empty_like(t["v"]), torch.empty_like(t["v"])
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    need = lib.frwkv_sm100_wkv7_prefill_workspace_bytes(n_seq, tokens, heads)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+    call = (t["cu_seqlens"].data_ptr(), t["state_indices"].data_ptr(), 0, t["state_pool"].data_ptr(),
+            t["r"].data_ptr(), t["w"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), t["a"].data_ptr(),
+            t["b"].data_ptr(), 0, 0, 0, 0, gate.data_ptr(), r_k.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(),
+            x.data_ptr(), y.data_ptr(), 0, n_seq, tokens, heads, _lib.IO_BF16, _lib.DECAY_RETENTION, 1.0,
+            max(wl.lengths), _lib.PREFILL_AUTO, ws.data_ptr(), need, err.data_ptr(), stream)
+
+    def prefill_step(i):
+        rc = lib.frwkv_sm100_wkv7_prefill_readout(*call)
+        if rc:
+            raise RuntimeError(_lib.last_error())
+
+    ms_per_step, repeats = _timed_region(prefill_step, args.steps, args.warmup, fdist)
+    token_heads = tokens * heads
+    algo = token_heads * (7 * 128 + 6 * 128) + n_seq * heads * 32768
+    achieved = algo / (ms_per_step * 1e-3) / 1e9
+    out["prefill_c2"] = {"value": round(tokens / (ms_per_step * 1e-3), 1), "unit": "tokens/s",
+                         "ms_per_step": round(ms_per_step, 6), "repeats": repeats,
+                         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                                      "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": algo},
+                         "kernels": "wkv7_chunk32_tc_kernel + wkv7_readout_rows_kernel (two launches; y round trip)",
+                         "error_flag": int(err.item())}
     del wl, t
     torch.cuda.empty_cache()
     return out

@@ -29,6 +29,7 @@ SYMBOLS = (
     "frwkv_sm100_wkv7_recurrent_fused_gate",
     "frwkv_sm100_wkv7_prefill_fused_gate",
     "frwkv_sm100_wkv7_recurrent_readout",
+    "frwkv_sm100_wkv7_prefill_readout",
 )
 
 _lib = None
@@ -78,6 +79,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_prefill_fused_gate.argtypes = [vp] * 15 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     lib.frwkv_sm100_wkv7_recurrent_readout.restype = ci
     lib.frwkv_sm100_wkv7_recurrent_readout.argtypes = [vp] * 21 + [ci, ci, ci, ci, ci, cf, ci, vp]
+    lib.frwkv_sm100_wkv7_prefill_readout.restype = ci
+    lib.frwkv_sm100_wkv7_prefill_readout.argtypes = [vp] * 21 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
     return lib
 
 

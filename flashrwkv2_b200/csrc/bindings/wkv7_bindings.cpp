@@ -505,8 +505,9 @@ void tmix_wkv7_fused_gate_fp32(torch::Tensor query_start_loc, torch::Tensor stat
       error_flag.has_value() ? error_flag->data_ptr<int>() : nullptr, stream));
 }
 
-// WKV7 with the readout's elementwise stage (head norm, r.k residual, output gate) as epilogue.  `output` receives
-// the gated result that feeds the output projection; `wkv_output` (y itself) is stored only when given.  With
+// WKV7 with the readout's elementwise stage (head norm, r.k residual, output gate): epilogue of the decode /
+// short-row kernel (strategy "decode"), or a second launch behind the prefill strategies.  `output` receives the
+// gated result that feeds the output projection; `wkv_output` (y itself) is stored only when given ("decode").  With
 // k_k, a0 and k_a the kk / a-gate producer is fused in as well: k is then the raw key, a the gate logits a12, and b
 // is not read.
 void tmix_wkv7_readout_fp32(torch::Tensor query_start_loc, torch::Tensor state_indices, torch::Tensor state,
@@ -516,8 +517,14 @@ void tmix_wkv7_readout_fp32(torch::Tensor query_start_loc, torch::Tensor state_i
                             double scale, std::optional<torch::Tensor> k_k, std::optional<torch::Tensor> a0,
                             std::optional<torch::Tensor> k_a, std::optional<torch::Tensor> decay_bias,
                             TicketPtr validated_metadata, int64_t max_seqlen, const std::string& decay_mode,
-                            std::optional<torch::Tensor> wkv_output, std::optional<torch::Tensor> output_f32) {
+                            std::optional<torch::Tensor> wkv_output, std::optional<torch::Tensor> output_f32,
+                            const std::string& strategy, std::optional<torch::Tensor> error_flag) {
   const int mode = decay_code(decay_mode);
+  TORCH_CHECK(strategy == "decode" || strategy == "auto" || strategy == "recurrent" || strategy == "chunk_tc",
+              "strategy must be 'decode', 'auto', 'recurrent' or 'chunk_tc'");
+  if (error_flag.has_value())
+    TORCH_CHECK(error_flag->is_cuda() && error_flag->scalar_type() == torch::kInt32 && error_flag->numel() >= 1,
+                "error_flag must be a CUDA int32 tensor");
   const bool fused = k_k.has_value() || a0.has_value() || k_a.has_value();
   TORCH_CHECK(!fused || (k_k.has_value() && a0.has_value() && k_a.has_value()),
               "k_k, a0 and k_a must be given together");
@@ -546,6 +553,28 @@ void tmix_wkv7_readout_fp32(torch::Tensor query_start_loc, torch::Tensor state_i
   const auto meta = resolve_metadata(query_start_loc, state_indices, state, r, validated_metadata, max_seqlen);
   const c10::cuda::CUDAGuard guard(state.device());
   const cudaStream_t stream = at::cuda::getCurrentCUDAStream(state.device().index()).stream();
+  if (strategy != "decode") {
+    // prefill strategies: the recurrence stores y, a second launch applies the readout stage to those rows
+    torch::Tensor y = wkv_output.has_value() ? *wkv_output : torch::empty_like(output);
+    const int strategy_code = strategy == "auto" ? FRWKV_PREFILL_AUTO
+                              : strategy == "recurrent" ? FRWKV_PREFILL_RECURRENT : FRWKV_PREFILL_CHUNK_TC;
+    const size_t need = frwkv_sm100_wkv7_prefill_workspace_bytes(static_cast<int>(dims.sequences),
+                                                                 static_cast<int>(r.size(0)),
+                                                                 static_cast<int>(dims.heads));
+    torch::Tensor workspace;
+    if (need > 0) workspace = torch::empty({static_cast<int64_t>(need)}, state.options().dtype(torch::kUInt8));
+    check_abi(frwkv_sm100_wkv7_prefill_readout(
+        meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), state.data_ptr<float>(),
+        r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+        fused ? nullptr : b->data_ptr(), fused ? k_k->data_ptr() : nullptr, fused ? a0->data_ptr() : nullptr,
+        fused ? k_a->data_ptr() : nullptr, decay_bias.has_value() ? decay_bias->data_ptr() : nullptr,
+        out_gate.data_ptr(), r_k.data_ptr(), ln_weight.data_ptr(), ln_bias.data_ptr(), output.data_ptr(), y.data_ptr(),
+        output_f32.has_value() ? output_f32->data_ptr<float>() : nullptr, static_cast<int>(dims.sequences),
+        static_cast<int>(r.size(0)), static_cast<int>(dims.heads), io_code(r), mode, static_cast<float>(scale),
+        static_cast<int>(meta.max_seqlen), strategy_code, need > 0 ? workspace.data_ptr() : nullptr, need,
+        error_flag.has_value() ? error_flag->data_ptr<int>() : nullptr, stream));
+    return;
+  }
   check_abi(frwkv_sm100_wkv7_recurrent_readout(
       meta.cu.data_ptr<int>(), meta.slots.data_ptr<int>(), meta.status.data_ptr<int>(), state.data_ptr<float>(),
       r.data_ptr(), decay_logits.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
@@ -647,7 +676,7 @@ void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_& module) {
              py::arg("k_k") = py::none(), py::arg("a0") = py::none(), py::arg("k_a") = py::none(),
              py::arg("decay_bias") = py::none(), py::arg("validated_metadata") = py::none(),
              py::arg("max_seqlen") = -1, py::arg("decay_mode") = "logits", py::arg("wkv_output") = py::none(),
-             py::arg("output_f32") = py::none());
+             py::arg("output_f32") = py::none(), py::arg("strategy") = "decode", py::arg("error_flag") = py::none());
   module.def("tmix_wkv7_prefill_fp32", &tmix_wkv7_prefill_fp32,
              "WKV7 chunked prefill taking cu_seqlens directly, fp32 state in place", py::arg("query_start_loc"),
              py::arg("state_indices"), py::arg("state"), py::arg("r"), py::arg("decay_logits"), py::arg("k"),

@@ -238,3 +238,40 @@ extern "C" int frwkv_sm100_wkv7_prefill_fused_gate(
                              max_seqlen, strategy, workspace, workspace_bytes, error_flag, gate,
                              static_cast<cudaStream_t>(stream));
 }
+
+namespace frwkv {
+int launch_readout_rows(const void* y, const void* r, const void* k, const void* v, const void* out_gate,
+                        const void* r_k, const void* ln_w, const void* ln_b, const void* const* gate, void* out,
+                        int total_tokens, int heads, int io_dtype, cudaStream_t stream);
+}
+
+extern "C" int frwkv_sm100_wkv7_prefill_readout(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* gate_k_k, const void* gate_a0, const void* gate_k_a, const void* decay_bias,
+    const void* out_gate, const void* r_k, const void* ln_weight, const void* ln_bias, void* out,
+    void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
+    int max_seqlen, int strategy, void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  using namespace frwkv;
+  const char* who = "wkv7_prefill_readout";
+  const int given = (gate_k_k != nullptr) + (gate_a0 != nullptr) + (gate_k_a != nullptr);
+  if (given != 0 && given != 3)
+    return fail(FRWKV_ERR_ARGUMENT, "%s: k_k, a0 and k_a must be given together or not at all", who);
+  if (!out_gate || !r_k || !ln_weight || !ln_bias || !out || !y)
+    return fail(FRWKV_ERR_ARGUMENT, "%s: out_gate, r_k, ln_weight, ln_bias, out and y must be non-null", who);
+  const void* more[] = {out_gate, r_k, ln_weight, ln_bias, out};
+  for (const void* q : more)
+    if ((reinterpret_cast<uintptr_t>(q) & 15) != 0)
+      return fail(FRWKV_ERR_ARGUMENT, "%s: tensors must be 16-byte aligned", who);
+  if (io_dtype == FRWKV_IO_FP32)
+    return fail(FRWKV_ERR_UNSUPPORTED, "%s: the readout stage takes float16 or bfloat16 tokens", who);
+  const void* gate[3] = {gate_k_k, gate_a0, gate_k_a};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = prefill_impl(who, cu_seqlens, slots, status, state_pool, r, w, k, v, a, b, decay_bias, y, y_f32, n_seq,
+                        total_tokens, heads, io_dtype, decay_mode, scale, max_seqlen, strategy, workspace,
+                        workspace_bytes, error_flag, given == 3 ? gate : nullptr, s);
+  if (rc != FRWKV_OK) return rc;
+  const void* producer[3] = {a, gate_a0, gate_k_a};  // the gate logits a12 travel in the a argument
+  return launch_readout_rows(y, r, k, v, out_gate, r_k, ln_weight, ln_bias, given == 3 ? producer : nullptr, out,
+                             total_tokens, heads, io_dtype, s);
+}

@@ -20,6 +20,10 @@
 //   delta = fp16(rho - 1 + dither(phase)),  phase = elapsed[slot] + head*64 + key + token offset,
 //   S = fp16(S + S*delta + b sa + k v^T) evaluated in fp32,  y = fp16(scale * r^T S) from the rounded state.
 // A key row is then 128 contiguous bytes and a lane moves 8 bytes of it per access; everything else is shared.
+//
+// One-token steps of large batches take the pipelined launch of the same kernel (recurrent_stream.cuh): a warp keeps
+// its head and column part, walks several sequences, and has the cp.async of its next state (8 KB into shared
+// memory, each lane copying what it reads back) in flight while it computes the current one.
 #include "recurrent_stream.cuh"
 
 namespace frwkv {

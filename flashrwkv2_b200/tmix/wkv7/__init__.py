@@ -199,7 +199,8 @@ def infer_tmix_wkv7_readout_fp32io16_forward_varlen(
         k_a: torch.Tensor | None = None, decay_bias: torch.Tensor | None = None, max_seqlen: int | None = None,
         validated_metadata: object | None = None, decay_mode: str = "logits",
         wkv_output: torch.Tensor | None = None, output_f32: torch.Tensor | None = None,
-        output_weight: torch.Tensor | None = None) -> torch.Tensor:
+        output_weight: torch.Tensor | None = None, strategy: str = "decode",
+        error_flag: torch.Tensor | None = None) -> torch.Tensor:
     """The in-place WKV7 recurrence followed, in the same kernel, by the elementwise stage of the reference's readout
     (flashrwkv2/tmix/readout/__init__.py:10-77: head normalisation with eps 64e-5, ``sum(r*k*r_k) * v`` residual,
     output gate): the recurrence's y never makes the round trip through HBM and r, k, v are not read a second time.
@@ -207,8 +208,10 @@ def infer_tmix_wkv7_readout_fp32io16_forward_varlen(
     Returns the gated tensor ``[T, H, 64]`` that feeds the output projection, or, when ``output_weight`` ``[C, C]`` is
     given, the projected ``[T, C]`` result (a plain library GEMM, as in the reference).  ``wkv_output`` and
     ``output_f32``, when given, also receive the recurrence's own y.  With ``k_k``, ``a0`` and ``k_a`` the kk / a-gate
-    producer is fused in as well (``k`` raw, ``a`` = gate logits a12, ``b`` ignored).  Serves decode steps and short
-    rows through the register-streaming kernel; long prefill rows run correctly but at that kernel's rate."""
+    producer is fused in as well (``k`` raw, ``a`` = gate logits a12, ``b`` ignored).  ``strategy="decode"`` (decode
+    steps and short rows) runs the stage as the epilogue of the register-streaming kernel; "auto", "chunk_tc" and
+    "recurrent" are the prefill strategies, behind which the stage is a second, HBM-bound launch over the stored y
+    rows (the tensor-core chunk kernel is bound by CUDA-core instructions, so it carries no epilogue)."""
     fused = k_k is not None or a0 is not None or k_a is not None
     if fused and (k_k is None or a0 is None or k_a is None):
         raise ValueError("k_k, a0 and k_a must be given together")
@@ -228,7 +231,7 @@ def infer_tmix_wkv7_readout_fp32io16_forward_varlen(
     _extension().tmix_wkv7_readout_fp32(
         cu_seqlens, state_indices, state_pool, r, decay_logits, k, v, a, None if fused else b, gate, r_k, ln_weight,
         ln_bias, out, float(scale), k_k, a0, k_a, decay_bias, ticket, -1 if max_seqlen is None else int(max_seqlen),
-        decay_mode, wkv_output, output_f32)
+        decay_mode, wkv_output, output_f32, strategy, error_flag)
     if output_weight is not None:
         return torch.nn.functional.linear(out.reshape(out.shape[0], -1), output_weight)
     return out

@@ -142,10 +142,13 @@ int frwkv_sm100_wkv7_recurrent_fp16_state(
  * instead of host-built per-chunk metadata.  Same fail-closed rules as above.
  *   strategy   : FRWKV_PREFILL_AUTO picks the tensor-core kernel for 16-bit
  *                tokens and long rows, else the register-streaming recurrence;
- *   workspace  : device scratch of at least frwkv_sm100_wkv7_prefill_workspace_bytes() bytes
- *                (4 bytes per sequence for batches of 2..2048 sequences), used to hand the
- *                sequences to the SMs longest first; NULL is accepted and keeps the natural
- *                order (same results, a longer tail on ragged batches);
+ *   workspace  : device scratch of at least frwkv_sm100_wkv7_prefill_workspace_bytes() bytes, 16-byte aligned.
+ *                For batches of 2..2048 sequences it holds the length ranking (4 bytes per sequence), used to
+ *                hand the sequences to the SMs longest first, and, when the batch has more (sequence, head)
+ *                streams than the GPU has CTA slots, the header and per-stream flags of the chunk kernel's
+ *                work queue (persistent CTAs that take (stream, segment) tasks; a segment's state passes to the
+ *                next through the pool slot).  NULL is accepted and keeps the natural order with one CTA per
+ *                stream (same results, a longer tail on ragged batches and partly filled last waves);
  *   error_flag : optional device int32; the tensor-core kernel ORs in bit 0 if one of its bounded waits gave up
  *                (that (sequence, head)'s rows of y are then NaN and its state slot keeps its old value) and bit 1
  *                if a chunk's decay product left the fp32 range (retention mode only; the output is then invalid).
@@ -205,6 +208,18 @@ int frwkv_sm100_wkv7_recurrent_readout(
     const void* out_gate, const void* r_k, const void* ln_weight, const void* ln_bias, void* out,
     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
     int max_seqlen, void* stream);
+
+/* Prefill with the same readout stage.  The chunk kernel is bound by its CUDA-core instruction count, so here the stage
+ * is a second, HBM-bound launch over the rows the prefill stored (768 bytes per (token, head); with the fused producer
+ * the gated key is recomputed from the raw key and the gate logits): y is required as the intermediate.  Arguments as
+ * in frwkv_sm100_wkv7_recurrent_readout and frwkv_sm100_wkv7_prefill. */
+int frwkv_sm100_wkv7_prefill_readout(
+    const int32_t* cu_seqlens, const int32_t* slots, const int32_t* status, float* state_pool,
+    const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+    const void* gate_k_k, const void* gate_a0, const void* gate_k_a, const void* decay_bias,
+    const void* out_gate, const void* r_k, const void* ln_weight, const void* ln_bias, void* out,
+    void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
+    int max_seqlen, int strategy, void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
 
 #ifdef __cplusplus
 }
