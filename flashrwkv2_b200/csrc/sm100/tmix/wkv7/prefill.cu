@@ -34,6 +34,22 @@ constexpr int kShortRow = 16;  // rows shorter than this go to the recurrence ke
 constexpr int kMaxOrdered = 2048;
 constexpr int kOrderThreads = 1024;
 
+// Segments per stream that minimise ceil(N S / slots) / S * (1 + 1.5 S / chunks) for N streams of `chunks` chunks
+// (see sequence_order_kernel); shared by the kernel and by the host's choice of launch mode.
+__host__ __device__ inline int pick_segments(long long streams, int chunks_longest, int cta_slots) {
+  int best = 1;
+  float best_cost = 1e30f;
+  for (int S = 1; S <= chunk::kQueueLevels && S * 8 <= chunks_longest; ++S) {
+    const float rounds = static_cast<float>((streams * S + cta_slots - 1) / cta_slots) / S;
+    const float cost = rounds * (1.0f + 1.5f * S / chunks_longest);
+    if (cost < best_cost * 0.995f) {
+      best_cost = cost;
+      best = S;
+    }
+  }
+  return best;
+}
+
 __global__ void __launch_bounds__(kOrderThreads) sequence_order_kernel(const int* __restrict__ cu,
                                                                        const int* __restrict__ status, int n_seq,
                                                                        int* __restrict__ order, int heads, int len_from,
@@ -73,18 +89,8 @@ __global__ void __launch_bounds__(kOrderThreads) sequence_order_kernel(const int
   if (threadIdx.x == 0) {
     const int chunks_longest = max(1, (longest + 31) / 32);
     int best = 1;
-    if (live > 0 && shortest >= longest - longest / 10) {
-      float best_cost = 1e30f;
-      const long long streams = static_cast<long long>(live) * heads;
-      for (int S = 1; S <= chunk::kQueueLevels && S * 8 <= chunks_longest; ++S) {
-        const float rounds = static_cast<float>((streams * S + cta_slots - 1) / cta_slots) / S;
-        const float cost = rounds * (1.0f + 1.5f * S / chunks_longest);
-        if (cost < best_cost * 0.995f) {
-          best_cost = cost;
-          best = S;
-        }
-      }
-    }
+    if (live > 0 && shortest >= longest - longest / 10)
+      best = pick_segments(static_cast<long long>(live) * heads, chunks_longest, cta_slots);
     segment_chunks_shared = (chunks_longest + best - 1) / best;
   }
   __syncthreads();
@@ -133,7 +139,6 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
                     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode,
                     float scale, int max_seqlen, int len_from, void* workspace, size_t workspace_bytes,
                     int32_t* error_flag, const void* const* gate, cudaStream_t stream) {
-  (void)max_seqlen;
   const int32_t* order = nullptr;
   void* queue = nullptr;
   const size_t need = chunk_tc_workspace_bytes(n_seq, total_tokens, heads);
@@ -141,7 +146,13 @@ int launch_chunk_tc(const int32_t* cu, const int32_t* slots, const int32_t* stat
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0)
       return fail(FRWKV_ERR_WORKSPACE, "wkv7_prefill: workspace of %zu bytes (16-byte aligned) needed, got %zu", need,
                   workspace_bytes);
-    if (wants_queue(n_seq, heads)) {
+    // Persistent CTAs with the work queue pay a few per cent against one CTA per stream (task hand-out, no overlap
+    // of a CTA's tail with the next CTA's start), so they are used only where cutting streams into segments wins:
+    // uniform batches (every row max_seqlen long) for which the cost model picks more than one segment.  Ragged
+    // batches are balanced by the longest-first order alone.
+    const bool uniform = max_seqlen > 0 && static_cast<long long>(n_seq) * max_seqlen == total_tokens;
+    if (wants_queue(n_seq, heads) && uniform &&
+        pick_segments(static_cast<long long>(n_seq) * heads, (max_seqlen + 31) / 32, cta_slots()) > 1) {
       queue = static_cast<char*>(workspace) + order_bytes(n_seq);
       const size_t queue_bytes = sizeof(chunk::QueueHeader) + static_cast<size_t>(n_seq) * heads * sizeof(int);
       if (cudaMemsetAsync(queue, 0, queue_bytes, stream) != cudaSuccess) return check_launch("work-queue memset");

@@ -259,3 +259,39 @@ def test_c_abi_rejects_misaligned_tensors_before_any_launch():
         for kw in (dict(bias=base + 0x9002), dict(y32=base + 0xA004), dict(y=base + 0x8008)):
             assert call(entry, **kw) == 1, (entry, kw)
             assert "16-byte aligned" in _lib.last_error()
+
+
+def test_readout_entries_reject_bad_arguments_before_any_launch():
+    """The entries with the readout stage: missing or misaligned readout tensors, a partial set of gate parameters
+    and (prefill) a missing y come back as argument errors.  Made-up pointers: nothing is dereferenced or launched."""
+    from flashrwkv2_b200 import _lib
+
+    lib = _lib.load()
+    base = 0x7F0000000000
+    p = [base + 0x1000 * i for i in range(1, 20)]
+
+    def call(entry, gate=(0, 0, 0), ro=None, y=0, out=None):
+        ro = (p[10], p[11], p[12], p[13]) if ro is None else ro
+        out = p[14] if out is None else out
+        head = (p[0], p[1], 0, p[2], p[3], p[4], p[5], p[6], p[7], p[8], *gate, 0, *ro, out, y, 0, 4, 4, 2, _lib.IO_BF16,
+                _lib.DECAY_LOGITS, 1.0, 1)
+        if entry == "recurrent":
+            return lib.frwkv_sm100_wkv7_recurrent_readout(*head, 0)
+        return lib.frwkv_sm100_wkv7_prefill_readout(*head, _lib.PREFILL_AUTO, 0, 0, 0, 0)
+
+    for entry in ("recurrent", "prefill"):
+        assert call(entry, gate=(p[15], 0, p[16]), y=p[17]) == 1 and "together" in _lib.last_error()
+        assert call(entry, ro=(0, p[11], p[12], p[13]), y=p[17]) == 1 and "non-null" in _lib.last_error()
+        assert call(entry, ro=(p[10] + 2, p[11], p[12], p[13]), y=p[17]) == 1 and "aligned" in _lib.last_error()
+        assert call(entry, out=p[14] + 8, y=p[17]) == 1 and "aligned" in _lib.last_error()
+    assert call("prefill", y=0) == 1 and "y must be non-null" in _lib.last_error()
+
+
+def test_native_module_exports_the_fused_operators():
+    from flashrwkv2_b200 import _C_sm100 as ext
+
+    for name in ("tmix_wkv7_fused_gate_fp32", "tmix_wkv7_readout_fp32"):
+        assert hasattr(ext, name), name
+    head = ext.tmix_wkv7_readout_fp32.__doc__.splitlines()[0]
+    for arg in ("out_gate", "r_k", "ln_weight", "ln_bias", "wkv_output", "strategy", "error_flag"):
+        assert arg + ":" in head, arg

@@ -433,9 +433,9 @@ def test_prefill_operator_under_cuda_graph_capture():
 def test_work_queue_hands_the_state_from_segment_to_segment(lengths):
     """More streams than the GPU has CTA slots (10 sequences x 30 heads = 300 > 296): the chunk kernel runs with
     persistent CTAs that take (stream, segment) tasks.  Equal lengths are cut into several segments (300 streams on
-    296 slots would otherwise take two rounds) whose state passes through the pool slot; the ragged batch keeps whole
-    streams in longest-first order.  Against the C oracle, and bit-identical to the same call without scratch (one
-    CTA per stream, no queue)."""
+    296 slots would otherwise take two rounds) whose state passes through the pool slot; the ragged batch is left to
+    the longest-first order with one CTA per stream.  Against the C oracle, and bit-identical to the same call without
+    scratch (one CTA per stream, natural order, no queue)."""
     from flashrwkv2_b200 import _lib
 
     case = _random_case(lengths, 30, torch.bfloat16, seed=404, slots=[3, 9, 0, 7, 1, 8, 2, 6, 4, 5], pool_slots=11)
