@@ -156,6 +156,11 @@ def build_testhooks(force: bool = False) -> Path:
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     TEST_LIB.parent.mkdir(parents=True, exist_ok=True)
     srcs = sources()
+    # a library built from exactly these sources (it travels with the tree, the objects do not) is used as it is
+    stamp = TEST_LIB.parent / ".objects"
+    wanted = "\n".join(f"{s.stem}.hooks.{_digest(s)}.o" for s in srcs)
+    if TEST_LIB.exists() and stamp.exists() and stamp.read_text() == wanted and not force:
+        return TEST_LIB
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, False, ("-DFRWKV_TEST_HOOKS",), ".hooks"), srcs))
     return _link(TEST_LIB, objs, TEST_LIB.parent / ".objects", force)

@@ -2,6 +2,8 @@
 // instantiate them (recurrent_stream.cu: the fp32- and fp16-state contracts and the fused kk/a-gate input form;
 // recurrent_readout.cu: the forms with the readout epilogue).  See recurrent_stream.cu for the design.
 #pragma once
+// Compile-time tuning: sequences per warp of the pipelined one-token launch (the grid is that much deeper than the
+// resident CTAs), and whether the plain recurrence takes that launch too (the fused forms always may).
 #ifndef FRWKV_PIPELINE_DEPTH
 #define FRWKV_PIPELINE_DEPTH 3
 #endif
@@ -196,8 +198,8 @@ wkv7_recurrent_stream_kernel(const RecurrentParams p) {
     return;
   }
   const int active = min(p.status != nullptr ? p.status[2] : p.n_seq, p.n_seq);
-  // Work items.  Plain launch: one (sequence, head, column part) per warp.  PIPELINED launch (one-token steps of the
-  // kernels that do more per token than move the state): the grid is a whole number of "sequence lanes" of
+  // Work items.  Plain launch: one (sequence, head, column part) per warp.  PIPELINED launch (one-token steps of
+  // large batches): the grid is a whole number of "sequence lanes" of
   // heads * PARTS warps; a warp keeps its head and part and walks the sequences lane by lane, and the state of its
   // next sequence travels to shared memory (cp.async, 16 bytes per lane and row: each lane copies exactly what it
   // reads back) while the current one is computed, so that the warp always has a state in flight.

@@ -111,7 +111,15 @@ def infer_tmix_wkv7_prefill_fp32io16_forward_varlen(
     """Same contract for long and ragged rows: chunks on the tensor cores, state carried in fp32, in
     place on ``state_pool``.  The reference has no operator with this signature (its chunk operator
     takes host-built per-chunk metadata and returns a new pool: see
-    :func:`flashrwkv2_b200.tmix.wkv7.rl_infctx.rl_infctx_tmix_wkv7_chunk_fp32io16`)."""
+    :func:`flashrwkv2_b200.tmix.wkv7.rl_infctx.rl_infctx_tmix_wkv7_chunk_fp32io16`).
+
+    ``strategy``: "auto" (tensor-core chunk kernel for 16-bit tokens and rows of 16 tokens or more, the recurrence
+    for the rest), "chunk_tc" or "recurrent".  Limits of the chunk kernel: it agrees with the fp32 recurrence to
+    1-2.5e-3 of the output's RMS (5e-3 is the stated gate); in ``decay_mode="retention"`` the product of the
+    retentions over a 32-row chunk must stay above 1e-36 (any retention RWKV-7 can produce, >= 0.545 per token, does).
+    ``error_flag`` (one int32 on the device, zeroed by the caller) receives bit 1 when that range is left (the
+    output is then invalid) and bit 0 when a bounded device wait gave up (that (sequence, head)'s rows are NaN and its
+    state slot keeps its old value)."""
     return _launch("tmix_wkv7_prefill_fp32", (r, decay_logits, k, v, a, b), state_pool=state_pool,
                    cu_seqlens=cu_seqlens, state_indices=state_indices, scale=scale, decay_bias=decay_bias,
                    max_seqlen=max_seqlen, validated_metadata=validated_metadata,

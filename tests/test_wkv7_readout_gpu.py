@@ -290,3 +290,65 @@ def test_readout_oracle_against_the_reference_kernel():
     want = readout_prelinear_oracle(view(y), view(r), view(k), view(v), r_k.cpu(), ln_w.cpu(), ln_b.cpu(), view(gate))
     excess = (view(out).float() - want).abs() - 1.01 * _half_ulp(want, torch.float16)
     assert float(excess.max() / want.square().mean().sqrt()) <= 2e-5
+
+
+def test_pipelined_decode_under_a_capacity_ticket_and_graph_replay():
+    """The decode step as serving runs it: captured once in a CUDA graph with a capacity ticket (160 sequences x 64
+    heads: the pipelined launch), replayed after the live metadata changed to 100 active sequences.  Each replay must
+    equal, bit for bit, the eager call on exactly the active sequences."""
+    import flashrwkv2_b200.tmix.wkv7 as ops
+
+    cap, heads = 160, 64
+    case = _case((1,) * cap, heads, torch.float16, seed=77, bias=True)
+    d = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    initial = d["state_pool"].clone()
+    pool = initial.clone()
+    cu = d["cu_seqlens"].clone()
+    slots = d["state_indices"].clone()
+    n_tok = torch.full((1,), cap, dtype=torch.int32, device=DEV)
+    n_seq = torch.full((1,), cap, dtype=torch.int32, device=DEV)
+    common = dict(gate=d["gate"], r_k=d["r_k"], ln_weight=d["ln_weight"], ln_bias=d["ln_bias"], scale=case["scale"],
+                  decay_bias=d["decay_bias"])
+    tokens = ("r", "w", "k", "v", "a", "b")
+    stream = torch.cuda.Stream()
+
+    def captured_call():
+        ticket = ops.prepare_tmix_wkv7_recurrent_metadata(
+            cu, slots, state_pool_size=pool.shape[0], token_capacity=cap, sequence_capacity=cap,
+            max_seqlen_capacity=1, num_active_tokens=n_tok, num_active_sequences=n_seq)
+        return ops.infer_tmix_wkv7_readout_fp32io16_forward_varlen(
+            *(d[n] for n in tokens), state_pool=pool, cu_seqlens=cu, state_indices=slots, validated_metadata=ticket,
+            **common)
+
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        captured_call()  # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    pool.copy_(initial)
+    with torch.cuda.graph(graph, stream=stream):
+        out = captured_call()
+
+    def eager(active):
+        fresh = initial.clone()
+        got = ops.infer_tmix_wkv7_readout_fp32io16_forward_varlen(
+            *(d[n][:active] for n in tokens), state_pool=fresh,
+            cu_seqlens=torch.arange(active + 1, dtype=torch.int32, device=DEV),
+            state_indices=d["state_indices"][:active].contiguous(),
+            **{**common, "gate": d["gate"][:active]})
+        torch.cuda.synchronize()
+        return got, fresh
+
+    for active in (cap, 100):
+        pool.copy_(initial)
+        cu.copy_(torch.cat([torch.arange(active + 1, dtype=torch.int32), torch.full((cap - active,), -1, dtype=torch.int32)]))
+        live = d["state_indices"].clone()
+        live[active:] = 10 ** 6
+        slots.copy_(live)
+        n_tok.fill_(active)
+        n_seq.fill_(active)
+        graph.replay()
+        torch.cuda.synchronize()
+        want, want_pool = eager(active)
+        assert torch.equal(out[:active], want) and torch.equal(pool, want_pool)
