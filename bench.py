@@ -58,11 +58,12 @@ ALGO_FLOP_PREFILL_TOKEN_HEAD = 98304  # 12 GEMMs of 64^3 per 64 rows
 ALGO_BYTES_PREFILL_TOKEN_HEAD = 7 * 128
 ALGO_BYTES_PREFILL_PAIR = 32768
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# DRAM bytes of one launch (read + written) per unit of work, from ncu captures (profiles/): decode per
-# (sequence, head), from captures of the c4_decode launch itself (131,072 pairs); prefill per (token, head), from a
-# capture of the c2 launch (traffic grows in proportion to the units).  Reads equal the algorithmic bytes; the
-# state written by the last CTAs is still dirty in L2 when a kernel ends, so the totals are 1-2 % below them.
-DECODE_TRAFFIC_PER_PAIR = 4.354e9 / 131072
+# DRAM bytes of one launch (read + written) from ncu captures (profiles/): decode from captures of the c4_decode
+# launch itself (131,072 pairs) and of the c1 launch (8,192 pairs); the other forms per (sequence, head) of their
+# c4-sized captures; prefill per (token, head), from a capture of the c2 launch (traffic grows in proportion to the
+# units).  Reads equal the algorithmic bytes; the state written by the last CTAs is still dirty in L2 when a kernel
+# ends, so the totals are a little below them.
+DECODE_DIRTY_IN_L2_BYTES = 58.0e6  # 4.412 GB algorithmic - 4.354 GB measured (c4); 275.8 MB - 217.2 MB (c1)
 DECODE_FP16_STATE_TRAFFIC_PER_PAIR = 2.211e9 / 131072
 DECODE_READOUT_TRAFFIC_PER_PAIR = 4.383e9 / 131072
 PREFILL_TRAFFIC_PER_TOKEN_HEAD = (809.58e6 + 127.15e6) / (32768 * 32)
@@ -186,7 +187,9 @@ def _timed_region(step, steps, warmup, fdist):
 def _roofline(name, kind, peaks, peak_kind, ms_per_step, pairs, token_heads):
     if kind == "decode":
         algo = pairs * ALGO_BYTES_DECODE_PAIR
-        traffic = int(pairs * DECODE_TRAFFIC_PER_PAIR)
+        # reads are counted in full; of the state a launch writes, what is still dirty in L2 when the kernel ends
+        # (about 58 MB in both captures: the 8,192-pair c1 launch and the 131,072-pair c4 launch) is not
+        traffic = int(max(pairs * (16384 + 6 * 128), pairs * ALGO_BYTES_DECODE_PAIR - DECODE_DIRTY_IN_L2_BYTES))
         kernel = "wkv7_recurrent_stream_kernel"
     else:
         algo = token_heads * ALGO_BYTES_PREFILL_TOKEN_HEAD + pairs * ALGO_BYTES_PREFILL_PAIR

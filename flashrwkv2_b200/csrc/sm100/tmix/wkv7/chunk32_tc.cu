@@ -82,7 +82,7 @@ static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one S
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColP = 0, kColQ = 64, kColU = 128, kColS = 192;
 
-template <typename io_t, bool LOGITS, bool FUSED>
+template <typename io_t, bool LOGITS, bool FUSED, bool QUEUE>
 __global__ void __launch_bounds__(kThreads, 2)
 wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   extern __shared__ uint8_t smem_raw[];
@@ -100,7 +100,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   }
   const int active = p.status != nullptr ? p.status[2] : p.n_seq;
   // The stream (sequence, head) and the range of its rows this CTA works on.  Direct mode: one stream per CTA, all of
-  // its rows.  Queue mode (p.queue != nullptr): CTAs are persistent and take (stream, segment) tasks from a counter;
+  // its rows.  Queue mode (QUEUE): CTAs are persistent and take (stream, segment) tasks from a counter;
   // a segment is a run of `segment chunks` 32-row chunks, the state travels from a segment to the next through the
   // pool slot, and a per-stream flag says how many segments are complete (see QueueHeader in chunk_common.cuh).
   int head = 0, t_begin = 0, len = 0, n_chunks = 0, slot = 0, segment = 0;
@@ -412,23 +412,24 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
   // ---- next task ------------------------------------------------------------------------------------------
   // every warp has left the previous task; if that one was aborted (the compute warps carry `failed`), everybody
   // leaves the loop together
-  if (__syncthreads_or(failed ? 1 : 0) != 0) break;
-  if (tid == 0) {
-    int task = -1;
-    if (p.queue != nullptr) {
-      task = atomicAdd(&p.queue->next_task, 1);
-      if (task >= p.queue->total_tasks) task = -1;
-    } else if (first_task) {
-      task = static_cast<int>(blockIdx.x);
+  int task;
+  if constexpr (QUEUE) {
+    if (__syncthreads_or(failed ? 1 : 0) != 0) break;
+    if (tid == 0) {
+      int next = atomicAdd(&p.queue->next_task, 1);
+      if (next >= p.queue->total_tasks) next = -1;
+      *task_word = next;
     }
-    *task_word = task;
+    __syncthreads();
+    task = *task_word;
+    if (task < 0) break;
+  } else {  // one CTA per (sequence, head): a single pass
+    if (!first_task) break;
+    task = static_cast<int>(blockIdx.x);
   }
-  __syncthreads();
-  const int task = *task_word;
-  if (task < 0) break;
   {
     int rank;
-    if (p.queue != nullptr) {
+    if (QUEUE) {
       // tasks are numbered segment by segment; the streams that have a segment g are the first level_end[g] -
       // level_end[g-1] ranks of the longest-first order, all heads of a rank next to each other
       int g = 0;
@@ -447,7 +448,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     if (seq >= active || seq < 0 || seq >= p.n_seq) continue;
     const int seq_begin = p.cu[seq], seq_len = p.cu[seq + 1] - seq_begin;
     if (seq_len <= 0 || seq_len < p.len_from) continue;
-    const int seg_rows = p.queue != nullptr ? p.queue->segment_chunks * kChunk : seq_len;
+    const int seg_rows = QUEUE ? p.queue->segment_chunks * kChunk : seq_len;
     t_begin = seq_begin + segment * seg_rows;
     len = min(seq_len - segment * seg_rows, seg_rows);
     if (len <= 0) continue;
@@ -455,7 +456,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     n_chunks = (len + kChunk - 1) / kChunk;
     slot = p.slots[seq];
     state_g = p.pool + (static_cast<size_t>(slot) * p.heads + head) * (kHeadDim * kHeadDim);
-    segments_done = p.queue != nullptr ? p.queue_flags + static_cast<size_t>(seq) * p.heads + head : nullptr;
+    segments_done = QUEUE ? p.queue_flags + static_cast<size_t>(seq) * p.heads + head : nullptr;
     bias_g = LOGITS && p.bias != nullptr ? static_cast<const io_t*>(p.bias) + head * kHeadDim : nullptr;
     if constexpr (FUSED) {
       const int at = head * kHeadDim + 2 * lane;
@@ -483,7 +484,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     // ---- queue mode, later segment: the previous segment of this stream must have stored its state.  Its task
     // was handed out before this one, so the CTA that took it is running or done: the wait ends, and is bounded
     // anyway.  The flag is read with acquire semantics by one thread; the barrier passes the ordering on.
-    if (segment > 0) {
+    if (QUEUE && segment > 0) {
       if (tid == 0) {
         int seen = 0;
         for (int poll = 0; poll < (1 << 22); ++poll) {
@@ -799,7 +800,7 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
     }
     // queue mode: the state of this segment is in the pool slot (stored by all compute threads before the barrier
     // that ended the last chunk): publish it
-    if (!failed && segments_done != nullptr && tid == 0) {
+    if (QUEUE && !failed && segments_done != nullptr && tid == 0) {
       __threadfence();
       const int done = segment + 1;
       asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(segments_done), "r"(done) : "memory");
@@ -896,13 +897,13 @@ wkv7_chunk32_tc_kernel(const ChunkParams p, const __grid_constant__ Maps maps) {
 }
 
 // The shared-memory attribute is set once per device and kernel instance, not on every call.
-template <typename io_t, bool LOGITS, bool FUSED>
+template <typename io_t, bool LOGITS, bool FUSED, bool QUEUE>
 int prepare_kernel() {
   static bool done[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return check_launch("cudaGetDevice");
   if (!done[device]) {
-    if (cudaFuncSetAttribute(wkv7_chunk32_tc_kernel<io_t, LOGITS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(wkv7_chunk32_tc_kernel<io_t, LOGITS, FUSED, QUEUE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes) != cudaSuccess)
       return check_launch("wkv7_chunk32_tc_kernel shared-memory attribute");
     done[device] = true;  // benign race: two threads may both set the same attribute
@@ -910,14 +911,14 @@ int prepare_kernel() {
   return FRWKV_OK;
 }
 
-template <typename io_t, bool FUSED>
+template <typename io_t, bool FUSED, bool QUEUE>
 int launch_typed32(const ChunkParams& p, const Maps& maps, bool logits, cudaStream_t stream) {
-  const int rc = logits ? prepare_kernel<io_t, true, FUSED>() : prepare_kernel<io_t, false, FUSED>();
+  const int rc = logits ? prepare_kernel<io_t, true, FUSED, QUEUE>() : prepare_kernel<io_t, false, FUSED, QUEUE>();
   if (rc != FRWKV_OK) return rc;
-  auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true, FUSED> : wkv7_chunk32_tc_kernel<io_t, false, FUSED>;
+  auto kernel = logits ? wkv7_chunk32_tc_kernel<io_t, true, FUSED, QUEUE> : wkv7_chunk32_tc_kernel<io_t, false, FUSED, QUEUE>;
   long long ctas = static_cast<long long>(p.n_seq) * p.heads;
   if (ctas > 0x7fffffffLL) return fail(FRWKV_ERR_ARGUMENT, "wkv7_prefill: too many (sequence, head) pairs");
-  if (p.queue != nullptr) {  // persistent CTAs, two per SM
+  if constexpr (QUEUE) {  // persistent CTAs, two per SM
     int device = 0, sms = 148;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -962,12 +963,17 @@ int launch_chunk32_tc(const int32_t* cu, const int32_t* slots, const int32_t* st
   p.skip_commit_chunk = chunk::test_skip_commit_chunk();
 #endif
   const bool logits = decay_mode == FRWKV_DECAY_LOGITS;
+  const bool queued = queue != nullptr;
   if (gate != nullptr) {
-    if (bf16) return launch_typed32<__nv_bfloat16, true>(p, maps, logits, stream);
-    return launch_typed32<__half, true>(p, maps, logits, stream);
+    if (bf16) return queued ? launch_typed32<__nv_bfloat16, true, true>(p, maps, logits, stream)
+                            : launch_typed32<__nv_bfloat16, true, false>(p, maps, logits, stream);
+    return queued ? launch_typed32<__half, true, true>(p, maps, logits, stream)
+                  : launch_typed32<__half, true, false>(p, maps, logits, stream);
   }
-  if (bf16) return launch_typed32<__nv_bfloat16, false>(p, maps, logits, stream);
-  return launch_typed32<__half, false>(p, maps, logits, stream);
+  if (bf16) return queued ? launch_typed32<__nv_bfloat16, false, true>(p, maps, logits, stream)
+                          : launch_typed32<__nv_bfloat16, false, false>(p, maps, logits, stream);
+  return queued ? launch_typed32<__half, false, true>(p, maps, logits, stream)
+                : launch_typed32<__half, false, false>(p, maps, logits, stream);
 }
 
 }  // namespace frwkv

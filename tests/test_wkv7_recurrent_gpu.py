@@ -220,6 +220,42 @@ def test_pipelined_decode_launch(dtype, retention):
         assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("heads,n_seq", [(1, 2400), (3, 800), (5, 500), (7, 350), (40, 130), (64, 40)])
+def test_pipelined_launch_shapes_equal_the_plain_launch(heads, n_seq):
+    """Head counts that do and do not divide the resident warps, with sequence counts just above two per warp: the
+    pipelined launch (forced through the test build) must reproduce the plain launch bit for bit, touch every
+    sequence exactly once and leave the unused slots alone."""
+    from conftest import load_testhooks
+
+    from flashrwkv2_b200 import _lib
+
+    case = _random_case((1,) * n_seq, heads, torch.bfloat16, seed=heads, pool_slots=n_seq + 3)
+    d = _to_dev(case)
+    lib = load_testhooks()
+    results = []
+    for rounds in (2, 1000):
+        pool = d["state_pool"].clone()
+        y = torch.full_like(d["v"], float("nan"))
+        lib.frwkv_sm100_test_pipeline_min_rounds(rounds)
+        try:
+            rc = lib.frwkv_sm100_wkv7_recurrent(
+                d["cu_seqlens"].data_ptr(), d["state_indices"].data_ptr(), 0, pool.data_ptr(),
+                *(d[n].data_ptr() for n in TOKEN_NAMES), 0, y.data_ptr(), 0, n_seq, n_seq, heads, _lib.IO_BF16,
+                _lib.DECAY_RETENTION, case["scale"], 1, torch.cuda.current_stream().cuda_stream)
+        finally:
+            lib.frwkv_sm100_test_pipeline_min_rounds(0)
+        assert rc == 0
+        torch.cuda.synchronize()
+        results.append((y.cpu(), pool.cpu()))
+    (y_pipe, pool_pipe), (y_plain, pool_plain) = results
+    assert not torch.isnan(y_pipe.float()).any()
+    assert torch.equal(y_pipe, y_plain) and torch.equal(pool_pipe, pool_plain)
+    touched = set(case["state_indices"].tolist())
+    for slot in range(pool_pipe.shape[0]):
+        if slot not in touched:
+            assert torch.equal(pool_pipe[slot], case["state_pool"][slot])
+
+
 def test_run_to_run_bit_identical():
     case = _random_case((3, 1, 40, 7), 4, torch.bfloat16, seed=9)
     first = _run_op(case)
