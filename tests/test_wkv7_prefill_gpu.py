@@ -447,3 +447,19 @@ def test_work_queue_hands_the_state_from_segment_to_segment(lengths):
     y_direct, y32_direct, pool_direct, err_direct = _run_tc_c_abi(lib, case)  # passes no workspace
     assert int(err_direct.item()) == 0
     assert torch.equal(y, y_direct) and torch.equal(pool, pool_direct)
+
+
+@pytest.mark.parametrize("n_seq,heads,length", [(5, 64, 1056), (7, 48, 1500), (11, 32, 800), (20, 30, 331), (4, 128, 2048)])
+def test_queue_and_whole_stream_launches_agree_bit_for_bit(n_seq, heads, length):
+    """Uniform batches a little above one round of CTA slots, where the launcher's estimate sends some to the work
+    queue (several segment counts) and keeps others on one CTA per stream: whatever it picks must reproduce the call
+    without scratch (natural order, one CTA per stream) bit for bit, with no error bit."""
+    from flashrwkv2_b200 import _lib
+
+    case = _random_case((length,) * n_seq, heads, torch.bfloat16, seed=n_seq * heads)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y, y32, pool = _run_op(case, op="prefill", strategy="chunk_tc", error_flag=err)
+    assert int(err.item()) == 0 and not torch.isnan(y32).any()
+    y_direct, y32_direct, pool_direct, err_direct = _run_tc_c_abi(_lib.load(), case)
+    assert int(err_direct.item()) == 0
+    assert torch.equal(y, y_direct) and torch.equal(y32, y32_direct) and torch.equal(pool, pool_direct)
