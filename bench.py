@@ -203,6 +203,8 @@ def _roofline(name, kind, peaks, peak_kind, ms_per_step, pairs, token_heads):
         tflops = token_heads * ALGO_FLOP_PREFILL_TOKEN_HEAD / (ms_per_step * 1e-3) / 1e12
         out["tensor_tflops"] = round(tflops, 2)
         out["tensor_frac_of_bf16_peak"] = round(tflops / peaks["bf16_tflops"], 4)
+        # for reference: the flop the recurrence itself needs, 9 D^2 per (token, head), at the same time
+        out["recurrence_minimal_tflops"] = round(token_heads * 9 * 64 * 64 / (ms_per_step * 1e-3) / 1e12, 2)
     return out
 
 
