@@ -85,6 +85,12 @@ wkv7_decode_fp16_state_kernel(const DecodeParams p, const __grid_constant__ CUte
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long n_items = static_cast<long long>(p.n_seq) * p.heads;
 
+  // Programmatic dependent launch (see the launcher): this grid may be scheduled while the previous kernel of the
+  // stream drains, but nothing is read before that kernel has completed.  Without the launch attribute both
+  // instructions do nothing.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
   if (p.status != nullptr && p.status[0] != 0) {
     const float qnan = __int_as_float(0x7fffffff);
     const long long elements = static_cast<long long>(p.total_tokens) * p.heads * kHeadDim;
@@ -353,6 +359,8 @@ int prepare() {
 }  // namespace
 
 // One-token rows only (the caller guarantees max_seqlen == 1); pool_slots = number of slots of the pool.
+bool programmatic_launch_enabled();  // recurrent_stream.cu: FRWKV_PDL, read once
+
 int launch_decode_fp16_state(const int32_t* cu, const int32_t* slots, const int32_t* status, const int32_t* elapsed,
                              void* pool, int pool_slots, const void* r, const void* w, const void* k, const void* v,
                              const void* a, const void* b, const void* bias, void* y, int n_seq, int total_tokens,
@@ -386,10 +394,22 @@ int launch_decode_fp16_state(const int32_t* cu, const int32_t* slots, const int3
                  static_cast<const __half*>(v), static_cast<const __half*>(a), static_cast<const __half*>(b),
                  static_cast<const __half*>(bias), static_cast<__half*>(y), error_flag, n_seq, total_tokens, heads,
                  scale};
-  if (logits)
-    wkv7_decode_fp16_state_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p, map);
-  else
-    wkv7_decode_fp16_state_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p, map);
+  // A decode step is this kernel and the counter kernel behind it, step after step on one stream: both are launched
+  // with programmatic stream serialisation, so that each one's launch and ramp hide under its predecessor's tail
+  // (every kernel of the chain waits for its predecessor's completion before it touches memory).
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = programmatic_launch_enabled() ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t err = logits ? cudaLaunchKernelEx(&config, wkv7_decode_fp16_state_kernel<true>, p, map)
+                                 : cudaLaunchKernelEx(&config, wkv7_decode_fp16_state_kernel<false>, p, map);
+  if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "wkv7_decode_fp16_state_kernel: %s", cudaGetErrorString(err));
   return check_launch("wkv7_decode_fp16_state_kernel");
 }
 

@@ -46,6 +46,10 @@ namespace {
 // recurrence: invalid metadata leaves every counter untouched.
 __global__ void advance_elapsed_kernel(const int* __restrict__ cu, const int* __restrict__ slots,
                                        const int* __restrict__ status, int* __restrict__ elapsed, int n_seq) {
+  // scheduled early under the recurrence kernel's tail (programmatic dependent launch), it waits here for that
+  // kernel to complete: only then may a counter change
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (status != nullptr && status[0] != 0) return;
   const int active = status != nullptr ? status[2] : n_seq;
   const int seq = blockIdx.x * blockDim.x + threadIdx.x;
@@ -53,6 +57,9 @@ __global__ void advance_elapsed_kernel(const int* __restrict__ cu, const int* __
   elapsed[slots[seq]] += cu[seq + 1] - cu[seq];
 }
 }  // namespace
+
+// FRWKV_PDL=0 (read once) turns programmatic dependent launch off everywhere.
+bool programmatic_launch_enabled() { return pdl_enabled(); }
 
 // Shared argument checks of the recurrent and prefill entries.
 int check_wkv7_arguments(const char* who, const int32_t* cu, const int32_t* slots, float* pool,
@@ -144,7 +151,21 @@ int launch_recurrent_fp16_state(const int32_t* cu, const int32_t* slots, const i
     rc = dispatch_parts<__half, __half>(p, decay_mode == FRWKV_DECAY_LOGITS, parts, prefetch, stream);
   }
   if (rc != FRWKV_OK) return rc;
-  advance_elapsed_kernel<<<(n_seq + 255) / 256, 256, 0, stream>>>(cu, slots, status, elapsed, n_seq);
+  // launched so that it is scheduled under the recurrence kernel's tail; it waits for that kernel's completion
+  // (griddepcontrol.wait) before it touches a counter
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((n_seq + 255) / 256);
+  config.blockDim = dim3(256);
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, advance_elapsed_kernel, static_cast<const int*>(cu),
+                                             static_cast<const int*>(slots), static_cast<const int*>(status), elapsed,
+                                             n_seq);
+  if (err != cudaSuccess) return fail(FRWKV_ERR_CUDA, "advance_elapsed_kernel: %s", cudaGetErrorString(err));
   return check_launch("advance_elapsed_kernel");
 }
 
