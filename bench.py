@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload c4|c1|c2|c3|c4_decode|c4_prefill] [--no-extras] [--no-e2e]
-                    [--extra fp16_state|fused_gate|readout|gpu_baseline] [--min-region-s S]
+                    [--extra fp16_state|fused_gate|readout|pretrain|gpu_baseline] [--min-region-s S]
 
 Default workload ``c4``: the 7B-width batch sharded by sequence over the N GPUs of one box (strong scaling: the
 total work is fixed, every rank keeps the sequences the longest-first sharder gives it, all sliced from the one
@@ -539,6 +539,49 @@ def measure_readout(args, local_rank):
     return out
 
 
+def measure_pretrain(args, local_rank):
+    """The WKV7 training operator (forward with checkpoints + backward) on a dense 8 x 4096 x H32 bf16 batch, next to
+    the reference's own training kernels on the same tensors when oracle/_ref holds them.  CUDA-core kernels bound by
+    the per-token chain; reported for completeness of the operator family."""
+    import torch
+
+    import flashrwkv2_b200
+    from oracle.build_ref import load_ref
+
+    device = torch.device("cuda", local_rank)
+    batch, tokens, heads = 8, 4096, 32
+    g = torch.Generator(device=device).manual_seed(29)
+    shape = (batch, tokens, heads, 64)
+    rnd = lambda: torch.randn(shape, generator=g, device=device)
+    r, k, v = (rnd().mul_(0.5).bfloat16() for _ in range(3))
+    w = rnd().mul_(3.0).bfloat16()
+    kk = torch.nn.functional.normalize(rnd(), dim=-1)
+    a, b = (-kk).bfloat16(), (kk * torch.sigmoid(rnd())).bfloat16()
+    dy = rnd().bfloat16()
+    out = {"workload": f"dense B={batch} T={tokens} H={heads} D=64 bf16, zero initial state"}
+    modules = [("this_build", flashrwkv2_b200._C)]
+    try:
+        ref = load_ref()
+    except (ImportError, OSError):
+        ref = None
+    if ref is not None and hasattr(ref, "pretrain_tmix_wkv7_recurrent_forward"):
+        modules.append(("reference_kernels", ref))
+    for label, module in modules:
+        y = torch.empty_like(r)
+        boundary = torch.empty(batch, heads, tokens // 16, 64, 64, device=device)
+        sa = torch.empty(shape, device=device)
+        grads = [torch.empty_like(r) for _ in range(6)]
+        forward = lambda i: module.pretrain_tmix_wkv7_recurrent_forward(r, w, k, v, a, b, y, boundary, sa, 64)
+        backward = lambda i: module.pretrain_tmix_wkv7_recurrent_backward(r, w, k, v, a, b, dy, boundary, sa, *grads, 64)
+        times = []
+        for fn in (forward, backward):
+            fn(0)
+            times.append(_event_time_ms(fn, 5) / 5)
+        out[label] = {"forward_ms": round(times[0], 3), "backward_ms": round(times[1], 3),
+                      "tokens_per_s_forward_backward": round(batch * tokens / (sum(times) * 1e-3), 1)}
+    return out
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
 
@@ -587,6 +630,11 @@ def run_ours(args, rank, local_rank, world):
             extras["readout_epilogue"] = measure_readout(args, local_rank)
         except Exception as error:  # noqa: BLE001
             extras["readout_epilogue"] = {"error": str(error)}
+        try:
+            extras["pretrain"] = measure_pretrain(args, local_rank)
+        except Exception as error:  # noqa: BLE001
+            extras["pretrain"] = {"error": str(error)}
+        torch.cuda.empty_cache()
         torch.cuda.empty_cache()
         try:
             extras["gpu_baseline"] = gpu_baseline(torch.device("cuda", local_rank))
@@ -793,7 +841,7 @@ def main():
     parser.add_argument("--workload", default="c4", choices=("c4", "c1", "c2", "c3", "c4_decode", "c4_prefill"))
     parser.add_argument("--no-extras", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
-    parser.add_argument("--extra", default=None, choices=("fp16_state", "fused_gate", "readout", "gpu_baseline"),
+    parser.add_argument("--extra", default=None, choices=("fp16_state", "fused_gate", "readout", "pretrain", "gpu_baseline"),
                         help="one GPU: measure only this block of the default run's extras and print it")
     parser.add_argument("--min-region-s", type=float, default=MIN_REGION_S,
                         help="shortest timed region (default 0.5 s); 0 for a profiler capture of a few launches")
@@ -832,6 +880,7 @@ def main():
         block = {"fp16_state": lambda: measure_fp16_state_decode(args, local_rank),
                  "fused_gate": lambda: measure_fused_gate(args, local_rank),
                  "readout": lambda: measure_readout(args, local_rank),
+                 "pretrain": lambda: measure_pretrain(args, local_rank),
                  "gpu_baseline": lambda: gpu_baseline(torch.device("cuda", local_rank))}[args.extra]()
         print(json.dumps({"extra": args.extra, **block}), flush=True)
         fdist.shutdown()

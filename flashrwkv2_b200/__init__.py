@@ -53,6 +53,7 @@ from .tmix.wkv7 import (  # noqa: E402
     infer_tmix_wkv7_recurrent_fp16_forward_varlen,
     infer_tmix_wkv7_recurrent_fp32io16_forward_varlen,
     prepare_tmix_wkv7_recurrent_metadata,
+    pretrain_tmix_wkv7_recurrent_bf16,
     rl_infctx_tmix_wkv7_chunk_fp32io16,
 )
 
@@ -63,5 +64,6 @@ __all__ = [
     "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",
     "prepare_tmix_wkv7_recurrent_metadata",
+    "pretrain_tmix_wkv7_recurrent_bf16",
     "rl_infctx_tmix_wkv7_chunk_fp32io16",
 ]

@@ -30,6 +30,8 @@ SYMBOLS = (
     "frwkv_sm100_wkv7_prefill_fused_gate",
     "frwkv_sm100_wkv7_recurrent_readout",
     "frwkv_sm100_wkv7_prefill_readout",
+    "frwkv_sm100_wkv7_pretrain_forward",
+    "frwkv_sm100_wkv7_pretrain_backward",
 )
 
 _lib = None
@@ -81,6 +83,10 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.frwkv_sm100_wkv7_recurrent_readout.argtypes = [vp] * 21 + [ci, ci, ci, ci, ci, cf, ci, vp]
     lib.frwkv_sm100_wkv7_prefill_readout.restype = ci
     lib.frwkv_sm100_wkv7_prefill_readout.argtypes = [vp] * 21 + [ci, ci, ci, ci, ci, cf, ci, ci, vp, sz, vp, vp]
+    lib.frwkv_sm100_wkv7_pretrain_forward.restype = ci
+    lib.frwkv_sm100_wkv7_pretrain_forward.argtypes = [vp] * 9 + [ci, ci, ci, vp]
+    lib.frwkv_sm100_wkv7_pretrain_backward.restype = ci
+    lib.frwkv_sm100_wkv7_pretrain_backward.argtypes = [vp] * 15 + [ci, ci, ci, vp]
     return lib
 
 

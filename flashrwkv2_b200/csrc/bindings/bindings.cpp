@@ -6,6 +6,7 @@ void register_flashrwkv2_bindings(py::module_& module) {
 #if defined(FLASHRWKV_BACKEND_SM100)
   register_infer_tmix_wkv7_recurrent_fp32io16_bindings(module);
   register_rl_infctx_tmix_wkv7_chunk_forward_bindings(module);
+  register_pretrain_tmix_wkv7_recurrent_bindings(module);
 #else
 #error "this tree builds the SM100 backend only: define FLASHRWKV_BACKEND_SM100"
 #endif

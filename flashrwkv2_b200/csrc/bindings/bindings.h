@@ -8,3 +8,4 @@
 void register_flashrwkv2_bindings(py::module_& module);
 void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_& module);
 void register_rl_infctx_tmix_wkv7_chunk_forward_bindings(py::module_& module);
+void register_pretrain_tmix_wkv7_recurrent_bindings(py::module_& module);

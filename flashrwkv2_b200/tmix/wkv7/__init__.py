@@ -245,6 +245,7 @@ def infer_tmix_wkv7_readout_fp32io16_forward_varlen(
     return out
 
 
+from .pretrain import pretrain_tmix_wkv7_recurrent_bf16  # noqa: E402
 from .rl_infctx import rl_infctx_tmix_wkv7_chunk_fp32io16  # noqa: E402
 
 __all__ = [
@@ -254,5 +255,6 @@ __all__ = [
     "infer_tmix_wkv7_recurrent_fp16_forward_varlen",
     "infer_tmix_wkv7_recurrent_fp32io16_forward_varlen",
     "prepare_tmix_wkv7_recurrent_metadata",
+    "pretrain_tmix_wkv7_recurrent_bf16",
     "rl_infctx_tmix_wkv7_chunk_fp32io16",
 ]

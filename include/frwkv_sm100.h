@@ -221,6 +221,22 @@ int frwkv_sm100_wkv7_prefill_readout(
     void* y, float* y_f32, int n_seq, int total_tokens, int heads, int io_dtype, int decay_mode, float scale,
     int max_seqlen, int strategy, void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
 
+/* WKV7 training operator (dense [B, T, H, 64] bf16 tensors, T a multiple of 16, zero initial state, decay logits):
+ * the forward and backward passes behind the reference's pretrain_tmix_wkv7_recurrent_bf16
+ * (flashrwkv2/tmix/wkv7/pretrain.py:52-116; csrc/sm120/tmix/wkv7/pretrain_recurrent_bf16_forward.cu; oracle
+ * tests/tmix/wkv7/pretrain/test.py:44-65).  Stand in for its native symbols pretrain_tmix_wkv7_recurrent_forward /
+ * _backward with the same saved tensors:
+ *   boundary     : fp32 [B, H, T/16, 64, 64], the state after every 16th token;
+ *   state_dot_a  : fp32 [B, T, H, 64], a^T S_{t-1} of every token;
+ *   dy, dr .. db : bf16 [B, T, H, 64]. */
+int frwkv_sm100_wkv7_pretrain_forward(const void* r, const void* w, const void* k, const void* v, const void* a,
+                                      const void* b, void* y, float* boundary, float* state_dot_a, int batch,
+                                      int tokens, int heads, void* stream);
+int frwkv_sm100_wkv7_pretrain_backward(const void* r, const void* w, const void* k, const void* v, const void* a,
+                                       const void* b, const void* dy, const float* boundary,
+                                       const float* state_dot_a, void* dr, void* dw, void* dk, void* dv, void* da,
+                                       void* db, int batch, int tokens, int heads, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

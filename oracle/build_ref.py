@@ -40,6 +40,8 @@ REFERENCE_SOURCES = (
     "csrc/sm120/tmix/wkv7/infer_recurrent_fp16_forward_varlen.cu",
     "csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu",  # producer of a, b and the gated key
     "csrc/sm120/tmix/readout/infer_fp16_forward_varlen.cu",  # consumer of y: head norm, r.k residual, gate
+    "csrc/sm120/tmix/wkv7/pretrain_recurrent_bf16_forward.cpp",  # the training operator: forward + backward
+    "csrc/sm120/tmix/wkv7/pretrain_recurrent_bf16_forward.cu",
 )
 
 
@@ -63,7 +65,10 @@ def build_ref(checkout: str | os.PathLike, force: bool = False) -> Path | None:
     OUT.mkdir(parents=True, exist_ok=True)
     inc = [f"-I{d}" for d in cpp_extension.include_paths(device_type="cuda")]
     inc.append(f"-I{sysconfig.get_paths()['include']}")
+    # -D_N_ / -D_CHUNK_LEN_: the compile-time head size and checkpoint distance of the reference's training kernels
+    # (its setup.py passes the same two values)
     defs = ["-DTORCH_EXTENSION_NAME=_C_ref", "-DTORCH_API_INCLUDE_EXTENSION_H", "-DFLASHRWKV_BACKEND_SM120=1",
+            "-D_N_=64", "-D_CHUNK_LEN_=16",
             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}"]
     env = dict(os.environ)
     env.pop("CC", None)

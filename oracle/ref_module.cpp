@@ -10,6 +10,7 @@
 void register_infer_tmix_wkv7_recurrent_fp32io16_bindings(py::module_&);
 void register_rl_infctx_tmix_wkv7_chunk_forward_bindings(py::module_&);
 void register_infer_tmix_wkv7_recurrent_fp16_bindings(py::module_&);
+void register_pretrain_tmix_wkv7_recurrent_bindings(py::module_&);  // the training operator (forward + backward)
 // host launcher of the reference's kk/a-gate kernels
 // (csrc/sm120/tmix/wkv_prepare/internal/kk_a_gate/infer_fp16_forward_varlen.cu:209-260); its own binding lives in the
 // wkv_prepare operator, which is not built here
@@ -29,6 +30,7 @@ PYBIND11_MODULE(_C_ref, module) {
   register_infer_tmix_wkv7_recurrent_fp32io16_bindings(module);
   register_rl_infctx_tmix_wkv7_chunk_forward_bindings(module);
   register_infer_tmix_wkv7_recurrent_fp16_bindings(module);
+  register_pretrain_tmix_wkv7_recurrent_bindings(module);
   module.def("tmix_kk_a_gate_forward_varlen", &tmix_kk_a_gate_forward_varlen_cuda, py::arg("batch_size"),
              py::arg("max_seqlen"), py::arg("total_tokens"), py::arg("channels"), py::arg("heads"), py::arg("head_size"),
              py::arg("k"), py::arg("k_k"), py::arg("a0"), py::arg("a12"), py::arg("k_a"), py::arg("new_k"),

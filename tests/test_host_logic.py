@@ -295,3 +295,32 @@ def test_native_module_exports_the_fused_operators():
     head = ext.tmix_wkv7_readout_fp32.__doc__.splitlines()[0]
     for arg in ("out_gate", "r_k", "ln_weight", "ln_bias", "wkv_output", "strategy", "error_flag"):
         assert arg + ":" in head, arg
+
+
+def test_training_operator_contract_without_a_gpu():
+    """Signature and native argument names of the reference's training operator
+    (rwkv-rs/FlashRWKV2 flashrwkv2/tmix/wkv7/pretrain.py:117-133, pretrain_recurrent_bf16_forward.cpp:51-62), and the
+    wrapper's rejections, which come before the backend is touched."""
+    import inspect
+
+    import torch
+
+    from flashrwkv2_b200 import _C_sm100 as ext
+    from flashrwkv2_b200.tmix.wkv7.pretrain import pretrain_tmix_wkv7_recurrent_bf16 as op
+
+    assert tuple(inspect.signature(op).parameters) == ("r", "w", "k", "v", "a", "b", "head_size")
+    forward = ext.pretrain_tmix_wkv7_recurrent_forward.__doc__.splitlines()[0]
+    backward = ext.pretrain_tmix_wkv7_recurrent_backward.__doc__.splitlines()[0]
+    for name in ("r", "w", "k", "v", "a", "b", "output", "boundary", "state_dot_a", "head_size"):
+        assert f"{name}:" in forward, name
+    for name in ("grad_output", "boundary", "state_dot_a", "grad_r", "grad_w", "grad_k", "grad_v", "grad_a", "grad_b"):
+        assert f"{name}:" in backward, name
+    x = torch.zeros(1, 16, 64, dtype=torch.bfloat16)
+    with pytest.raises(TypeError, match="bfloat16"):
+        op(x.float(), x, x, x, x, x)
+    with pytest.raises(ValueError, match="contiguous CUDA"):
+        op(x, x, x, x, x, x)
+    with pytest.raises(ValueError, match="head_size"):
+        op(x, x, x, x, x, x, head_size=48)
+    with pytest.raises(ValueError, match="shape"):
+        op(x[0], x, x, x, x, x)
