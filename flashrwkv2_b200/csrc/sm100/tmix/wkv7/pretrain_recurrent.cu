@@ -232,14 +232,27 @@ wkv7_pretrain_backward_kernel(const TrainParams p, const __nv_bfloat16* __restri
         dS[i][1] = fmaf(rho, dS[i][1], av * dsa.y);
       }
       const float g_a = row_reduce8(part_da, lane);
+      // The five row gradients of this token replace the token's own rows in shared memory (this warp's eight rows
+      // are read by this warp only, and every read of them is above) and leave for global memory, coalesced, when the
+      // chunk is done.
       if (writes_row) {
-        dr[row_at + my_row] = __float2bfloat16_rn(g_r);
-        dk[row_at + my_row] = __float2bfloat16_rn(g_k);
-        db[row_at + my_row] = __float2bfloat16_rn(g_b);
-        da[row_at + my_row] = __float2bfloat16_rn(g_a);
-        dw[row_at + my_row] = __float2bfloat16_rn(g_rho * s_dfac[tt][my_row]);
+        s_r[tt][my_row] = g_r;
+        s_k[tt][my_row] = g_k;
+        s_b[tt][my_row] = g_b;
+        s_a[tt][my_row] = g_a;
+        s_dfac[tt][my_row] = g_rho * s_dfac[tt][my_row];
       }
       if (warp == 0) *reinterpret_cast<__nv_bfloat162*>(dv + row_at + col) = __floats2bfloat162_rn(dvv.x, dvv.y);
+    }
+    __syncthreads();
+    for (int e = tid; e < kTrainChunk * 32; e += kTrainThreads) {  // two channels per thread and row
+      const int tt = e >> 5, c = (e & 31) * 2;
+      const long long at = ((static_cast<long long>(batch) * p.tokens + t0 + tt) * p.heads + head) * 64 + c;
+      *reinterpret_cast<__nv_bfloat162*>(dr + at) = __floats2bfloat162_rn(s_r[tt][c], s_r[tt][c + 1]);
+      *reinterpret_cast<__nv_bfloat162*>(dk + at) = __floats2bfloat162_rn(s_k[tt][c], s_k[tt][c + 1]);
+      *reinterpret_cast<__nv_bfloat162*>(db + at) = __floats2bfloat162_rn(s_b[tt][c], s_b[tt][c + 1]);
+      *reinterpret_cast<__nv_bfloat162*>(da + at) = __floats2bfloat162_rn(s_a[tt][c], s_a[tt][c + 1]);
+      *reinterpret_cast<__nv_bfloat162*>(dw + at) = __floats2bfloat162_rn(s_dfac[tt][c], s_dfac[tt][c + 1]);
     }
   }
 }
