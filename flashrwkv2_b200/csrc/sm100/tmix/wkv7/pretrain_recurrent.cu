@@ -191,7 +191,7 @@ wkv7_pretrain_backward_kernel(const TrainParams p, const __nv_bfloat16* __restri
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float rv = s_r[tt][row0 + i], kv = s_k[tt][row0 + i], bv = s_b[tt][row0 + i];
-        const float inv_rho = 1.0f / s_rho[tt][row0 + i];
+        const float inv_rho = __fdividef(1.0f, s_rho[tt][row0 + i]);  // rho in [0.545, 1): two units in the last place
         part_dr[i] = fmaf(dyv.x, S[i][0], dyv.y * S[i][1]);
         dS[i][0] = fmaf(rv, dyv.x, dS[i][0]);
         dS[i][1] = fmaf(rv, dyv.y, dS[i][1]);
