@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfrwkv_sm100.so"
 IO_BF16, IO_FP16, IO_FP32 = 0, 1, 2
 DECAY_LOGITS, DECAY_RETENTION = 0, 1
 PREFILL_AUTO, PREFILL_RECURRENT, PREFILL_CHUNK_TC = 0, 1, 2
-ABI_VERSION = 1
+ABI_VERSION = 2
 STATIC_POOL_SLOTS = 65536
 
 # every symbol include/frwkv_sm100.h declares

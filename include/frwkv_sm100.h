@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define FRWKV_SM100_ABI_VERSION 1
+#define FRWKV_SM100_ABI_VERSION 2 /* 2: fp16-state, fused-gate, readout and training entries added; the entries of 1 unchanged */
 
 /* token dtype of r,w,k,v,a,b,y */
 enum { FRWKV_IO_BF16 = 0, FRWKV_IO_FP16 = 1, FRWKV_IO_FP32 = 2 };
